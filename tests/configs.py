@@ -160,3 +160,87 @@ def porarax_random(seed: int) -> dict:
                                                                pick(0.5, 2.0, 7.0))
         layers.append(layer)
     return dict(architecture="Porarax", vocab=pick(50, 131, 300), width=pick(32, 44, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)), layers=layers)
+
+
+# ---- Sogazen ---------------------------------------------------------------------------------------------------
+def _s_left(heads, kv_heads, dim, scale, softcap, base, dims):
+    return dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=scale, softcap=softcap, rot=dict(base=base, dims=dims))
+
+
+def _s_right(heads, vdim, state, groups, norm_groups, conv):
+    return dict(heads=heads, vdim=vdim, state=state, groups=groups, norm_groups=norm_groups, conv=conv)
+
+
+def _s_parallel(left, right, mlp):
+    return dict(type="parallel", mixer=dict(left=left, right=right), mlp=mlp)
+
+
+def _s_wkv(heads, dim, mlp, decay_rank=None):
+    m = dict(heads=heads, dim=dim)
+    if decay_rank:
+        m["decay_rank"] = decay_rank
+    return dict(type="wkv", mixer=m, mlp=mlp)
+
+
+def _s_moe(experts, top, identity, ff):
+    return dict(kind="moe", router=dict(experts=experts, top=top, identity=identity), expert=dict(ff=ff))
+
+
+def _s_dense(ff, limit):
+    return dict(kind="dense", ff=ff, limit=limit)
+
+
+# A: a recurrent layer first; heads of 16 and 24 with a third of the dimensions rotated, then none; several key/value
+# heads; a cap so low that tanh bends every score; more identity outputs than experts; every output chosen; norm groups
+# that are neither 1 nor the state groups; two and five taps; a layer without feed-forward; a decay layer of 5 values
+SOGAZEN_A = dict(architecture="Sogazen", vocab=140, width=48, norm=dict(eps=1e-5), logit_softcap=8.0, layers=[
+    _s_wkv(3, 8, _s_moe(3, 2, 1, 20), decay_rank=5),
+    _s_parallel(_s_left(4, 2, 24, 0.3, 2.5, 100.0, 8), _s_right(3, 16, 8, 1, 3, 2), _s_dense(40, 1.5)),
+    _s_parallel(_s_left(3, 3, 16, 0.5, 50.0, 10000.0, 0), _s_right(4, 8, 24, 2, 1, 5), None),
+    _s_wkv(1, 40, _s_moe(2, 4, 2, 12)),
+    _s_parallel(_s_left(6, 1, 16, 0.25, 6.0, 5000.0, 16), _s_right(2, 24, 16, 2, 4, 3), _s_moe(2, 1, 3, 16)),
+])
+
+# B: widths that are no multiples of 8; heads of 64 (16-byte rows for the vector kernels of single tokens) fully rotated;
+# nine query heads on one key/value head (more than the split-key kernel of single tokens groups); one expert and no
+# identity output; a wkv layer with heads of 72 channels (three lanes' worth a column); a single tap
+SOGAZEN_B = dict(architecture="Sogazen", vocab=97, width=44, norm=dict(eps=1e-6), logit_softcap=30.0, layers=[
+    _s_parallel(_s_left(2, 1, 64, 0.11, 20.0, 1000000.0, 64), _s_right(4, 12, 16, 4, 2, 4), _s_moe(1, 1, 0, 24)),
+    _s_wkv(2, 72, _s_dense(36, 0.7), decay_rank=12),
+    _s_parallel(_s_left(9, 1, 20, 0.2, 4.0, 50.0, 6), _s_right(1, 20, 40, 1, 1, 1), _s_moe(5, 3, 2, 12)),
+    _s_wkv(5, 16, None),
+])
+
+SOGAZEN = {"SA": SOGAZEN_A, "SB": SOGAZEN_B}
+
+
+def sogazen_random(seed: int) -> dict:
+    """A Sogazen configuration drawn from `seed`: 2 to 5 layers of either kind in any order, with head counts, sizes, rotated
+    dimensions, caps, groups, taps, experts, identity outputs and constants all drawn (small: the plain model is slow)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    pick = lambda *v: v[int(rng.integers(len(v)))]
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        r = rng.random()
+        if r < 0.2:
+            mlp = None
+        elif r < 0.45:
+            mlp = _s_dense(pick(8, 20, 36, 64), pick(0.5, 2.0, 7.0))
+        else:
+            experts, ident = pick(1, 2, 3, 5, 8), pick(0, 0, 1, 2, 4)
+            mlp = _s_moe(experts, int(rng.integers(1, min(experts + ident, 4) + 1)), ident, pick(8, 12, 24, 40))
+        if rng.random() < 0.4:
+            layers.append(_s_wkv(pick(1, 2, 3, 5), pick(8, 16, 24, 32, 40, 64), mlp, decay_rank=pick(3, 8, 16)))
+            continue
+        kv, dim = pick(1, 2, 3), pick(8, 16, 24, 32, 64, 128)
+        groups = pick(1, 2)
+        heads = groups * pick(1, 2, 3)
+        vdim = pick(8, 12, 16, 32)
+        ng = pick(*[g for g in (1, 2, 3, 4, heads) if (heads * vdim) % g == 0])
+        layers.append(_s_parallel(
+            _s_left(kv * pick(1, 2, 4, 6, 9), kv, dim, float(dim ** -0.5 * rng.uniform(0.5, 2.0)), pick(2.0, 10.0, 20.0, 50.0),
+                    pick(50.0, 10000.0, 1000000.0), pick(0, 2, dim // 4 * 2, dim)),
+            _s_right(heads, vdim, pick(8, 16, 32, 40), groups, ng, pick(1, 2, 3, 4, 6)), mlp))
+    return dict(architecture="Sogazen", vocab=pick(50, 131, 300), width=pick(32, 44, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)),
+                logit_softcap=pick(5.0, 30.0), layers=layers)

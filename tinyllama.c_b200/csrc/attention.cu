@@ -164,12 +164,15 @@ extern "C" int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int l
 // and sum, and every lane owns the output dims lane, lane+32, ...  Any head size up to
 // 32*MAXD, any number of heads and groups.
 #define ATT_MAXD 8
+// score <- cap * tanh(score / cap) where a cap is given (cap > 0)
+__device__ __forceinline__ float capped_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, T* __restrict__ out, int H, int KV,
-                      int hd, float scale, int window, int out_ld) {
+                      int hd, float scale, int window, int out_ld, float softcap, int sink) {
   tlc_pdl(q, k_pages, v_pages, out);
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -197,7 +200,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
       const T* kr = k_pages + (((size_t)page * KV + g) * TLC_PAGE + kp % TLC_PAGE) * hd;
       float dot = 0.f;
       for (int d = 0; d < hd; d++) dot = fmaf(to_f32(kr[d]), qs[d], dot);
-      s = dot;
+      s = capped_score(dot, softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = kp < n_keys ? expf(s - m_new) : 0.f;
@@ -219,6 +222,12 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
     }
     m = m_new;
   }
+  if (sink) {                               // one more term of score 0 in the denominator; it carries no value
+    const float m_new = fmaxf(m, 0.f), corr = expf(m - m_new);
+    l = l * corr + expf(-m_new);
+#pragma unroll
+    for (int i = 0; i < ATT_MAXD; i++) acc[i] *= corr;
+  }
   const float inv = 1.0f / l;
   T* o = out + (size_t)t * out_ld + (size_t)h * hd;
 #pragma unroll
@@ -231,7 +240,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
 extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                              const int* block_table, int max_pages, const int* positions, const int* row_seq,
                              const int* slots, void* out, int T, int H, int KV, int hd, float scale, int window,
-                             int out_ld, cudaStream_t stream) {
+                             int out_ld, float softcap, int sink, cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
@@ -240,7 +249,7 @@ extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, cons
   const size_t smem = (size_t)4 * hd * sizeof(float);
   TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(attention_warp_kernel<TT>, dim3(grid), dim3(128), smem, stream, 
       (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, (TT*)out,
-      H, KV, hd, scale, window, out_ld));
+      H, KV, hd, scale, window, out_ld, softcap, sink));
   TLC_CHECK_LAUNCH("attention");
   return 0;
 }
@@ -259,7 +268,8 @@ __global__ void __launch_bounds__(DEC_KEYS)
 attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                 const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                                 const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
-                                float* __restrict__ part_ml, int H, int KV, int hd, float scale, int window, int n_splits) {
+                                float* __restrict__ part_ml, int H, int KV, int hd, float scale, int window, int n_splits,
+                                float softcap) {
   tlc_pdl(q, k_pages, v_pages, part_o, part_ml);
   extern __shared__ float sh[];
   const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
@@ -296,7 +306,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
   }
   // per head: maximum and sum over the block's keys
   for (int hg = 0; hg < G; hg++) {
-    const float sv = valid ? s[hg] : -INFINITY;
+    const float sv = valid ? capped_score(s[hg], softcap) : -INFINITY;
     float m = warp_max(sv);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
@@ -336,7 +346,8 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
                                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                                     int max_pages, const int* __restrict__ positions, const int* __restrict__ row_seq,
                                     const int* __restrict__ slots, float* __restrict__ part_o,
-                                    float* __restrict__ part_ml, int H, int KV, float scale, int window, int n_splits) {
+                                    float* __restrict__ part_ml, int H, int KV, float scale, int window, int n_splits,
+                                    float softcap) {
   // Keys of earlier positions were stored by earlier steps; only the row at the query's own
   // position is written by the kernel before this one.  Everything else is fetched before the
   // wait on that kernel (see tlc_pdl).
@@ -407,6 +418,10 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
         }
       }
     }
+  }
+  if (softcap > 0.f) {
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++) s[hg] = capped_score(s[hg], softcap);
   }
   // maximum and sum over the block's keys, all heads of the group at once
   {
@@ -502,14 +517,14 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
 
 template <typename T>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              T* __restrict__ out, int hd, int n_splits, int H, int out_ld) {
+                                              T* __restrict__ out, int hd, int n_splits, int H, int out_ld, int sink) {
   tlc_pdl(part_o, part_ml, out);
   const size_t th = blockIdx.x;                       // row * H + head
   T* orow = out + (th / H) * (size_t)out_ld + (th % H) * (size_t)hd;
   const float* ml = part_ml + th * n_splits * 2;
-  float m = -INFINITY;
+  float m = sink ? 0.f : -INFINITY;           // (a sink is one more split: maximum 0, sum 1, no values)
   for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
-  float l = 0.f;
+  float l = sink ? expf(-m) : 0.f;
   for (int s = 0; s < n_splits; s++) if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
   const float inv = 1.0f / l;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
@@ -524,7 +539,8 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_pages, const void* v_pages,
                                     const int* block_table, int max_pages, const int* positions, const int* row_seq,
                                     const int* slots, void* out, float* part_o, float* part_ml, int T, int H, int KV,
-                                    int hd, float scale, int window, int max_keys, int out_ld, cudaStream_t stream) {
+                                    int hd, float scale, int window, int max_keys, int out_ld, float softcap, int sink,
+                                    cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
@@ -541,12 +557,12 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
     if (vsmem <= 48 * 1024) {
       const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
       if (hd == 64)
-        tlc_launch(attention_decode_partial_vec_kernel<64>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+        tlc_launch(attention_decode_partial_vec_kernel<64>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap);
       else if (hd == 128)
-        tlc_launch(attention_decode_partial_vec_kernel<128>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+        tlc_launch(attention_decode_partial_vec_kernel<128>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap);
       else
-        tlc_launch(attention_decode_partial_vec_kernel<256>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
-      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits, H, out_ld);
+        tlc_launch(attention_decode_partial_vec_kernel<256>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap);
+      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits, H, out_ld, sink);
       TLC_CHECK_LAUNCH("attention(decode)");
       return 0;
     }
@@ -554,8 +570,8 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
   TLC_DISPATCH_DTYPE(dtype, TT, {
     tlc_launch(attention_decode_partial_kernel<TT>, dim3(grid), dim3(DEC_KEYS), smem, stream, 
         (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, part_o,
-        part_ml, H, KV, hd, scale, window, n_splits);
-    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits, H, out_ld);
+        part_ml, H, KV, hd, scale, window, n_splits, softcap);
+    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits, H, out_ld, sink);
   });
   TLC_CHECK_LAUNCH("attention(decode)");
   return 0;
@@ -599,5 +615,5 @@ extern "C" int tlc_attention_decode_no_alloc(const void* q, int dtype, const voi
   float* part_o = g_decode_scratch_addr[dev];
   float* part_ml = part_o + (size_t)T * H * n_splits * hd;
   return tlc_attention_decode(q, dtype, k_pages, v_pages, block_table, max_pages, positions, row_seq, slots, out, part_o,
-                              part_ml, T, H, KV, hd, scale, window, max_keys, 0, stream);
+                              part_ml, T, H, KV, hd, scale, window, max_keys, 0, 0.f, 0, stream);
 }

@@ -148,12 +148,15 @@ template <bool QUICK> __device__ __forceinline__ float glu_act_of(int act, float
 // and up products and the pair's routing weight w.  w_out 0: the expert is fed the token scaled by w (gate and up are
 // linear, so w multiplies their results); 1: w multiplies what the expert returns (the down product is linear, so it
 // multiplies the activation).  act TLC_ACT_SILU / TLC_ACT_GELU_TANH: act(g) * u; TLC_ACT_SWISH_CLAMPED: with g cut off
-// above `limit` and u held within +-limit, g * sigmoid(alpha g) * (u + 1).
+// above `limit` and u held within +-limit, g * sigmoid(alpha g) * (u + 1); TLC_ACT_RELU_SQUARED: max(g, 0)^2, no u.
 template <bool QUICK> __device__ __forceinline__ float moe_pair_act(int act, int w_out, float limit, float alpha, float w, float g,
                                                                   float u) {
   if (!w_out) { g *= w; u *= w; }
   float y;
-  if (act == TLC_ACT_SWISH_CLAMPED) {
+  if (act == TLC_ACT_RELU_SQUARED) {         // an expert without a gate: u is not there
+    const float r = fmaxf(g, 0.f);
+    y = r * r;
+  } else if (act == TLC_ACT_SWISH_CLAMPED) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     const float sg = QUICK ? __fdividef(1.0f, 1.0f + __expf(-alpha * g)) : 1.0f / (1.0f + expf(-alpha * g));

@@ -319,7 +319,8 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z,
 template <int ACT> __device__ __forceinline__ float glu_act(float z) { return ACT == 1 ? gelu_tanh_f(z) : silu_f(z); }
 
 template <typename TI, typename T, int ACT>
-__global__ void glu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total, int interleave) {
+__global__ void glu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total, int interleave, float limit,
+                           float alpha) {
   tlc_pdl(gu, out);
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -327,21 +328,25 @@ __global__ void glu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restri
   const int f = (int)(i % F);
   const int gc = interleave ? (f >> 3) * 16 + (f & 7) : f, uc = interleave ? gc + 8 : F + f;
   const float g = to_f32(gu[t * ld + gc]), u = to_f32(gu[t * ld + uc]);
-  out[i] = from_f32<T>(glu_act<ACT>(g) * u);
+  if (ACT == TLC_ACT_SWISH_CLAMPED) out[i] = from_f32<T>(moe_pair_act<false>(ACT, 1, limit, alpha, 1.0f, g, u));
+  else out[i] = from_f32<T>(glu_act<ACT>(g) * u);
 }
 
 extern "C" int tlc_glu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave, int act,
-                       cudaStream_t stream) {
+                       float limit, float alpha, cudaStream_t stream) {
   const size_t total = (size_t)T * F;
   if (total == 0) return 0;
-  TLC_REQUIRE(act == 0 || act == 1, "glu: unknown activation %d (0 SiLU, 1 GELU in its tanh form)", act);
+  TLC_REQUIRE(act >= 0 && act <= 2, "glu: unknown activation %d (0 SiLU, 1 GELU in its tanh form, 2 the clamped swish)", act);
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (act == 1) {
+  if (act == 2) {
+    TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(glu_kernel<TI, TT, 2>, dim3(blocks), dim3(256), 0, stream,
+        (const TI*)gu, ld, F, (TT*)out, total, interleave, limit, alpha)));
+  } else if (act == 1) {
     TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(glu_kernel<TI, TT, 1>, dim3(blocks), dim3(256), 0, stream,
-        (const TI*)gu, ld, F, (TT*)out, total, interleave)));
+        (const TI*)gu, ld, F, (TT*)out, total, interleave, limit, alpha)));
   } else {
     TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(glu_kernel<TI, TT, 0>, dim3(blocks), dim3(256), 0, stream,
-        (const TI*)gu, ld, F, (TT*)out, total, interleave)));
+        (const TI*)gu, ld, F, (TT*)out, total, interleave, limit, alpha)));
   }
   TLC_CHECK_LAUNCH("glu");
   return 0;
@@ -349,7 +354,7 @@ extern "C" int tlc_glu(const void* gu, int in_dtype, int ld, int F, int T, void*
 
 extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave,
                           cudaStream_t stream) {
-  return tlc_glu(gu, in_dtype, ld, F, T, out, dtype, interleave, 0, stream);
+  return tlc_glu(gu, in_dtype, ld, F, T, out, dtype, interleave, 0, 0.f, 1.0f, stream);
 }
 
 // ---- RMSNorm with token shift --------------------------------------------------------------
@@ -480,5 +485,103 @@ extern "C" int tlc_gather_rows(const float* x, const int* rows, int R, int D, fl
   if (R == 0) return 0;
   tlc_launch(gather_rows_kernel, dim3(R), dim3(256), 0, stream, x, rows, D, out);
   TLC_CHECK_LAUNCH("gather_rows");
+  return 0;
+}
+
+// ---- a copy of 32-bit rows in the activation type, optionally through tanh ---------------------------------
+// Layers whose sublayers read the residual stream itself (no norm in front) take it from here in the type their
+// products want; act 1: tanh of every element first (the hidden layer of a small two-layer projection).
+template <typename TO>
+__global__ void convert_kernel(const float* __restrict__ x, int ldx, int D, TO* __restrict__ out, int ldo, size_t total, int act) {
+  tlc_pdl(x, out);
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / D;
+  const int d = (int)(i % D);
+  const float v = x[t * ldx + d];
+  out[t * ldo + d] = from_f32<TO>(act == 1 ? tanhf(v) : v);
+}
+extern "C" int tlc_convert(const float* x, int ldx, int T, int D, void* out, int dtype, int ldo, int act, cudaStream_t stream) {
+  const size_t total = (size_t)T * D;
+  if (total == 0) return 0;
+  TLC_REQUIRE(act == 0 || act == 1, "convert: unknown function %d (0 none, 1 tanh)", act);
+  TLC_DISPATCH_DTYPE(dtype, TO, tlc_launch(convert_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, ldx, D,
+                                           (TO*)out, ldo, total, act));
+  TLC_CHECK_LAUNCH("convert");
+  return 0;
+}
+
+// ---- x = cap * tanh(x / cap), in place -------------------------------------------------------------------------
+__global__ void softcap_kernel(float* x, size_t total, float cap) {
+  tlc_pdl(x);
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+extern "C" int tlc_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  TLC_REQUIRE(cap > 0.f, "softcap: the cap must be positive, got %g", (double)cap);
+  tlc_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, (size_t)n, cap);
+  TLC_CHECK_LAUNCH("softcap");
+  return 0;
+}
+
+// ---- the mean of several sublayers' results, each normed by itself ---------------------------------------------------
+// y = scale * sum_p parts[t, p, :] / sqrt(mean(parts[t, p, :]^2) + eps) * w[p, :]   (parts [T, n, D], w [n, D]);
+// then res[t] (+)= y, or with an outer weight wo: res[t] (+)= y / sqrt(mean(y^2) + eps_o) * wo.  One block per row; all
+// statistics 32-bit; y waits in shared memory for its scale where it fits, else it is formed twice.
+#define MEAN_MAX_PARTS 8
+__global__ void __launch_bounds__(1024)
+rmsnorm_mean_add_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ w, float eps, float scale,
+                        const float* __restrict__ wo, float eps_o, int D, float* __restrict__ res, int accumulate, int keep) {
+  tlc_pdl(parts, res);
+  __shared__ float red[33];
+  extern __shared__ float yrow[];
+  const int t = blockIdx.x;
+  const float* pr = parts + (size_t)t * n_parts * D;
+  float inv[MEAN_MAX_PARTS];
+#pragma unroll
+  for (int p = 0; p < MEAN_MAX_PARTS; p++) {
+    inv[p] = 0.f;
+    if (p < n_parts) {
+      float ss = 0.f;
+      for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = pr[(size_t)p * D + d]; ss += v * v; }
+      ss = block_sum(ss, red);
+      inv[p] = scale / sqrtf(ss / (float)D + eps);
+    }
+  }
+  auto mean_at = [&](int d) {
+    float y = 0.f;
+#pragma unroll
+    for (int p = 0; p < MEAN_MAX_PARTS; p++)
+      if (p < n_parts) y = fmaf(pr[(size_t)p * D + d] * inv[p], w[(size_t)p * D + d], y);
+    return y;
+  };
+  float s = 1.0f;
+  if (wo) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const float y = mean_at(d);
+      if (keep) yrow[d] = y;
+      ss += y * y;
+    }
+    ss = block_sum(ss, red);
+    s = 1.0f / sqrtf(ss / (float)D + eps_o);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float y = (wo && keep) ? yrow[d] : mean_at(d);          // (yrow[d] was written by this thread)
+    const float v = wo ? y * s * wo[d] : y;
+    float* o = res + (size_t)t * D + d;
+    *o = accumulate ? *o + v : v;
+  }
+}
+extern "C" int tlc_rmsnorm_mean_add(const float* parts, int n_parts, const float* w, float eps, float scale, const float* wo,
+                                    float eps_o, int T, int D, float* res, int accumulate, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(n_parts >= 1 && n_parts <= MEAN_MAX_PARTS, "rmsnorm_mean_add: %d summands (1..%d)", n_parts, MEAN_MAX_PARTS);
+  const int keep = (size_t)D * sizeof(float) <= 40 * 1024;
+  const int nt = (T < 256 && D >= 1024) ? 1024 : 256;
+  tlc_launch(rmsnorm_mean_add_kernel, dim3(T), dim3(nt), keep ? (size_t)D * sizeof(float) : 0, stream, parts, n_parts, w, eps, scale, wo,
+             eps_o, D, res, accumulate, keep);
+  TLC_CHECK_LAUNCH("rmsnorm_mean_add");
   return 0;
 }

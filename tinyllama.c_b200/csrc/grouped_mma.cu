@@ -31,7 +31,7 @@ __device__ __forceinline__ void gm_mma(float* c, uint32_t a0, uint32_t a1, uint3
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { GM_HEADS = 0, GM_GATE_UP = 1, GM_DOWN = 2 };
+enum { GM_HEADS = 0, GM_GATE_UP = 1, GM_DOWN = 2, GM_UP = 3 };      // GM_UP: an expert without a gate, act[i, f] = f(W[e] x[token(i)])
 
 struct GmArgs {
   const __nv_bfloat16* a;      // heads: [T, lda] with head h at h * a_hs; gate_up: x [T, lda]; down: act [pairs, K]
@@ -94,7 +94,7 @@ grouped_mma_kernel(GmArgs p) {
   for (int j = 0; j < WM; j++) {
     const int ar = (tid >> 2) + j * 32;
     if (MODE == GM_HEADS) a_src[j] = p.a + (size_t)group * p.a_hs + (size_t)min(row0 + ar, p.T - 1) * p.lda;
-    else if (MODE == GM_GATE_UP) a_src[j] = p.a + (size_t)(src_row[ar] / p.top) * p.lda;
+    else if (MODE == GM_GATE_UP || MODE == GM_UP) a_src[j] = p.a + (size_t)(src_row[ar] / p.top) * p.lda;
     else a_src[j] = p.a + (size_t)(row0 + min(ar, rows - 1)) * K;
     a_ok[j] = ar < rows;
   }
@@ -178,7 +178,7 @@ grouped_mma_kernel(GmArgs p) {
       float wgt = 1.0f;
       size_t orow;
       if (MODE == GM_HEADS) orow = (size_t)group * p.o_hs + (size_t)(row0 + rl) * p.ldo;
-      else if (MODE == GM_GATE_UP) { orow = (size_t)(row0 + rl) * N; wgt = p.wts[src_row[rl]]; }
+      else if (MODE == GM_GATE_UP || MODE == GM_UP) { orow = (size_t)(row0 + rl) * N; wgt = p.wts[src_row[rl]]; }
       else orow = (size_t)src_row[rl] * N;
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -187,7 +187,7 @@ grouped_mma_kernel(GmArgs p) {
           const int n = n0 + wn * 32 + 8 * j + 2 * q4 + c;
           if (n >= N) continue;
           const float v = acc[0][i][j][2 * e + c];
-          if (MODE == GM_GATE_UP) {
+          if (MODE == GM_GATE_UP || MODE == GM_UP) {
             const float u = acc[NW - 1][i][j][2 * e + c];
             reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] =
                 __float2bfloat16_rn(moe_pair_act<true>(p.act, p.w_out, p.limit, p.alpha, wgt, v, u));
@@ -240,7 +240,7 @@ extern "C" int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, cons
                                    const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
                                    int tile_rows, int act_code, int w_out, float limit, float alpha, cudaStream_t stream) {
   if (T == 0) return 0;
-  TLC_REQUIRE(act_code >= TLC_ACT_SILU && act_code <= TLC_ACT_SWISH_CLAMPED, "moe_experts_mma: unknown activation %d", act_code);
+  TLC_REQUIRE(act_code >= TLC_ACT_SILU && act_code <= TLC_ACT_RELU_SQUARED, "moe_experts_mma: unknown activation %d", act_code);
   TLC_REQUIRE(tile_rows == 32 || tile_rows == 64, "moe_experts_mma: tiles of %d rows are not built (32 or 64, as the routing was made)", tile_rows);
   TLC_REQUIRE(D % 8 == 0 && F % 8 == 0 && gm_aligned(x, ldx) && gm_aligned(wgu, D) && gm_aligned(wd, F) && gm_aligned(act, F),
               "moe_experts_mma: operands are not aligned for 16-byte copies");
@@ -250,7 +250,10 @@ extern "C" int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, cons
   p.order = order; p.offsets = offsets; p.tile_off = tile_off; p.wts = wts; p.E = E; p.top = top; p.T = T;
   p.act = act_code; p.w_out = w_out; p.limit = limit; p.alpha = alpha;
   p.a = (const __nv_bfloat16*)x; p.lda = ldx; p.w = (const __nv_bfloat16*)wgu; p.out = act; p.N = F; p.K = D;
-  if (tile_rows == 64) gm_launch<GM_GATE_UP, 2>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
+  if (act_code == TLC_ACT_RELU_SQUARED) {                   // no gate: wgu is [E, F, D], one product
+    if (tile_rows == 64) gm_launch<GM_UP, 2>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
+    else gm_launch<GM_UP, 1>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
+  } else if (tile_rows == 64) gm_launch<GM_GATE_UP, 2>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
   else gm_launch<GM_GATE_UP, 1>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
   TLC_CHECK_LAUNCH("moe_gate_up_mma");
   p.a = (const __nv_bfloat16*)act; p.lda = F; p.w = (const __nv_bfloat16*)wd; p.out = y; p.N = D; p.K = F;

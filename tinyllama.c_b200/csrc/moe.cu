@@ -21,19 +21,35 @@
 // lane finds the best of its experts (lane, lane + 32, ...) that come after the last choice in that order, and the
 // warp the best of the lanes.
 __global__ void __launch_bounds__(128)
-moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int mode, int* __restrict__ ids,
-                float* __restrict__ wts) {
+moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int mode, const float* __restrict__ choice_bias,
+                int* __restrict__ ids, float* __restrict__ wts) {
   tlc_pdl(logits, ids, wts);
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   const float* lr = logits + (size_t)t * ld;
   float last = INFINITY, first = 0.f, sum = 0.f;
   int last_e = -1;
+  // TLC_ROUTE_SOFTMAX_ALL: scores are the softmax over all E outputs; an expert is chosen by score + choice_bias[e] and
+  // weighted by the score alone
+  float all_max = 0.f, all_inv = 1.0f;
+  if (mode == TLC_ROUTE_SOFTMAX_ALL) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, lr[e]);
+    all_max = warp_max(m);
+    float s = 0.f;
+    for (int e = lane; e < E; e += 32) s += expf(lr[e] - all_max);
+    all_inv = 1.0f / warp_sum(s);
+  }
+  auto rank_of = [&](int e) {
+    if (mode != TLC_ROUTE_SOFTMAX_ALL) return lr[e];
+    const float s = __fmul_rn(expf(lr[e] - all_max), all_inv);      // (no contraction with the sum: the weight below is this s)
+    return choice_bias ? __fadd_rn(s, choice_bias[e]) : s;
+  };
   for (int k = 0; k < top; k++) {
     float best = -INFINITY;
     int be = 0x7fffffff;                     // none yet
     for (int e = lane; e < E; e += 32) {
-      const float v = lr[e];
+      const float v = rank_of(e);
       const bool after = v < last || (v == last && e > last_e);
       if (after && (be == 0x7fffffff || v > best)) { best = v; be = e; }   // (a lane's experts come in ascending order)
     }
@@ -52,11 +68,13 @@ moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
         const float e = expf(lr[be] - first);
         sum += e;
         wts[t * top + k] = e;
+      } else if (mode == TLC_ROUTE_SOFTMAX_ALL) {
+        wts[t * top + k] = __fmul_rn(expf(lr[be] - all_max), all_inv);
       } else {
         wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
       }
     }
-    last = lr[be];
+    last = best;                             // (the value the comparison saw, not one computed anew: the same bits)
     last_e = be;
   }
   if (mode == TLC_ROUTE_SOFTMAX && lane == 0) {
@@ -68,8 +86,8 @@ moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
 // One block sorts the pairs by expert: counts, offsets (and every expert's first tile of `tm` sorted rows), then the
 // list order [T*top]: pair index (t * top + k) of every sorted position.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int tm, int* __restrict__ order, int* __restrict__ offsets,
-                int* __restrict__ tile_off) {
+moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int E_tiled, int tm, int* __restrict__ order,
+                int* __restrict__ offsets, int* __restrict__ tile_off) {
   tlc_pdl(ids, order, offsets, tile_off);
   extern __shared__ int shi[];
   int* count = shi;            // [E]
@@ -85,7 +103,7 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int tm, int* __
       tile_off[e] = tiles;
       cursor[e] = o;
       o += count[e];
-      tiles += (count[e] + tm - 1) / tm;
+      if (e < E_tiled) tiles += (count[e] + tm - 1) / tm;       // (the others have no weights: no product visits them)
     }
     offsets[E] = o;
     tile_off[E] = tiles;
@@ -94,16 +112,17 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int tm, int* __
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
 }
 
-extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, int* ids, float* wts, int* order,
-                             int* offsets, int* tile_off, int tile_rows, cudaStream_t stream) {
+extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, const float* choice_bias, int n_identity,
+                             int* ids, float* wts, int* order, int* offsets, int* tile_off, int tile_rows, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(tile_rows >= 1, "moe_route: tiles of %d rows", tile_rows);
   TLC_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096, "moe_route: %d experts, %d chosen", E, top);
-  TLC_REQUIRE(mode == TLC_ROUTE_SIGMOID || mode == TLC_ROUTE_SOFTMAX, "moe_route: unknown weighting %d", mode);
-  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, mode, ids, wts);
+  TLC_REQUIRE(mode == TLC_ROUTE_SIGMOID || mode == TLC_ROUTE_SOFTMAX || mode == TLC_ROUTE_SOFTMAX_ALL, "moe_route: unknown weighting %d", mode);
+  TLC_REQUIRE(n_identity >= 0 && n_identity < E, "moe_route: %d of %d router outputs without an expert's weights", n_identity, E);
+  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, mode, choice_bias, ids, wts);
   TLC_CHECK_LAUNCH("moe_topk");
-  tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, tile_rows, order,
-             offsets, tile_off);
+  tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, E - n_identity, tile_rows,
+             order, offsets, tile_off);
   TLC_CHECK_LAUNCH("moe_sort");
   return 0;
 }
@@ -131,7 +150,7 @@ template <typename TA, typename TW, typename TO, bool QUICK>
 __global__ void __launch_bounds__(256)
 moe_gate_up_kernel(const TA* __restrict__ x, int ldx, const TW* __restrict__ wgu, const int* __restrict__ order,
                    const int* __restrict__ offsets, const int* __restrict__ tile_off, const float* __restrict__ wts, int E, int top,
-                   int F, int D, TO* __restrict__ act, int act_code, int w_out, float limit, float alpha) {
+                   int F, int D, TO* __restrict__ act, int act_code, int w_out, float limit, float alpha, int gated) {
   tlc_pdl(x, order, offsets, tile_off, wts, act);
   __shared__ float As[MOE_TK][MOE_TM + 1], Gs[MOE_TK][MOE_TN + 1], Us[MOE_TK][MOE_TN + 1];
   __shared__ int tok[MOE_TM];
@@ -140,8 +159,8 @@ moe_gate_up_kernel(const TA* __restrict__ x, int ldx, const TW* __restrict__ wgu
   const int n0 = blockIdx.y * MOE_TN;
   if (threadIdx.x < MOE_TM) tok[threadIdx.x] = threadIdx.x < rows ? order[row0 + threadIdx.x] / top : -1;
   __syncthreads();
-  const TW* wg = wgu + (size_t)e * 2 * F * D;
-  const TW* wu = wg + (size_t)F * D;
+  const TW* wg = wgu + (size_t)e * (gated ? 2 : 1) * F * D;      // (ungated experts: [E, F, D], one product)
+  const TW* wu = gated ? wg + (size_t)F * D : wg;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float g00 = 0.f, g01 = 0.f, g10 = 0.f, g11 = 0.f, u00 = 0.f, u01 = 0.f, u10 = 0.f, u11 = 0.f;
   for (int k0 = 0; k0 < D; k0 += MOE_TK) {
@@ -152,7 +171,7 @@ moe_gate_up_kernel(const TA* __restrict__ x, int ldx, const TW* __restrict__ wgu
       const int n = n0 + rr;
       const bool ok = n < F && k < D;
       Gs[kk][rr] = ok ? to_f32(wg[(size_t)n * D + k]) : 0.f;
-      Us[kk][rr] = ok ? to_f32(wu[(size_t)n * D + k]) : 0.f;
+      Us[kk][rr] = (ok && gated) ? to_f32(wu[(size_t)n * D + k]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -229,15 +248,16 @@ extern "C" int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* 
                                const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
                                void* act, int act_dtype, int act_code, int w_out, float limit, float alpha, cudaStream_t stream) {
   if (T == 0) return 0;
-  TLC_REQUIRE(act_code >= TLC_ACT_SILU && act_code <= TLC_ACT_SWISH_CLAMPED, "moe_gate_up: unknown activation %d", act_code);
+  TLC_REQUIRE(act_code >= TLC_ACT_SILU && act_code <= TLC_ACT_RELU_SQUARED, "moe_gate_up: unknown activation %d", act_code);
+  const int gated = act_code != TLC_ACT_RELU_SQUARED;
   dim3 grid(moe_max_tiles(T, E, top), (F + MOE_TN - 1) / MOE_TN);
   if (act_dtype == TLC_BF16) {
     TLC_DISPATCH_DTYPE(x_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_gate_up_kernel<TA, TW, __nv_bfloat16, true>, grid,
         dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (__nv_bfloat16*)act, act_code, w_out, limit,
-        alpha)));
+        alpha, gated)));
   } else {
     TLC_DISPATCH_DTYPE(x_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_gate_up_kernel<TA, TW, float, false>, grid,
-        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (float*)act, act_code, w_out, limit, alpha)));
+        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (float*)act, act_code, w_out, limit, alpha, gated)));
   }
   TLC_CHECK_LAUNCH("moe_gate_up");
   return 0;
@@ -250,5 +270,27 @@ extern "C" int tlc_moe_down(const void* act, int act_dtype, const void* wd, int 
   TLC_DISPATCH_DTYPE(act_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_down_kernel<TA, TW>, grid, dim3(256), 0, stream,
       (const TA*)act, (const TW*)wd, order, offsets, tile_off, E, F, D, y)));
   TLC_CHECK_LAUNCH("moe_down");
+  return 0;
+}
+
+// Router outputs without an expert's weights stand for experts that return their input: y[pair, :] = weight * x[token, :]
+// for every pair routed to an output >= E (no product visits those pairs).  A block per pair.
+template <typename TX>
+__global__ void __launch_bounds__(256)
+moe_identity_kernel(const TX* __restrict__ x, int ldx, const int* __restrict__ ids, const float* __restrict__ wts, int top, int E, int D,
+                    float* __restrict__ y) {
+  tlc_pdl(x, ids, wts, y);
+  const int pair = blockIdx.x;
+  if (ids[pair] < E) return;
+  const float w = wts[pair];
+  const TX* xr = x + (size_t)(pair / top) * ldx;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)pair * D + d] = w * to_f32(xr[d]);
+}
+extern "C" int tlc_moe_identity(const void* x, int x_dtype, int ldx, const int* ids, const float* wts, int T, int top, int E, int D,
+                                float* y, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_DISPATCH_DTYPE(x_dtype, TX, tlc_launch(moe_identity_kernel<TX>, dim3(T * top), dim3(256), 0, stream, (const TX*)x, ldx, ids, wts, top,
+                                             E, D, y));
+  TLC_CHECK_LAUNCH("moe_identity");
   return 0;
 }

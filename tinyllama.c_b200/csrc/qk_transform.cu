@@ -125,3 +125,32 @@ extern "C" int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int 
   TLC_CHECK_LAUNCH("gate_mul");
   return 0;
 }
+
+// ---- queries and keys normed over their whole width -----------------------------------------------------------------
+// In place on the 32-bit projection: the q_n query columns from q_off (all heads together) are divided by their root mean
+// square and multiplied by qw [q_n], the k_n key columns from k_off likewise with kw; before any rotation.  One block per row.
+__global__ void __launch_bounds__(256)
+qk_whole_norm_kernel(float* qkv, int ld, int q_off, int q_n, const float* __restrict__ qw, int k_off, int k_n,
+                     const float* __restrict__ kw, float eps) {
+  tlc_pdl(qkv);
+  __shared__ float red[33];
+  float* row = qkv + (size_t)blockIdx.x * ld;
+  for (int which = 0; which < 2; which++) {
+    float* x = row + (which ? k_off : q_off);
+    const int n = which ? k_n : q_n;
+    const float* w = which ? kw : qw;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < n; d += blockDim.x) { const float v = x[d]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int d = threadIdx.x; d < n; d += blockDim.x) x[d] = x[d] * s * w[d];
+  }
+}
+extern "C" int tlc_qk_whole_norm(float* qkv, int ld, int q_off, int q_n, const float* qw, int k_off, int k_n, const float* kw, float eps,
+                                 int T, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(q_n >= 1 && k_n >= 1, "qk_whole_norm: %d query and %d key columns", q_n, k_n);
+  tlc_launch(qk_whole_norm_kernel, dim3(T), dim3(256), 0, stream, qkv, ld, q_off, q_n, qw, k_off, k_n, kw, eps);
+  TLC_CHECK_LAUNCH("qk_whole_norm");
+  return 0;
+}

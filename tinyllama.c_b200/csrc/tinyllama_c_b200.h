@@ -31,8 +31,10 @@
 #define TLC_ACT_SILU 0       /* activations of gated products: z * sigmoid(z) */
 #define TLC_ACT_GELU_TANH 1  /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
 #define TLC_ACT_SWISH_CLAMPED 2 /* experts only: g = min(g, limit), u = clamp(u, -limit, limit): g sigmoid(alpha g) (u + 1) */
+#define TLC_ACT_RELU_SQUARED 3 /* experts without a gate: max(W_up h, 0)^2 */
 #define TLC_ROUTE_SIGMOID 0  /* a chosen expert's weight is the sigmoid of its logit */
 #define TLC_ROUTE_SOFTMAX 1  /* the chosen experts' weights are the softmax restricted to their own logits */
+#define TLC_ROUTE_SOFTMAX_ALL 2 /* scores are the softmax over ALL router outputs; chosen by score + a bias, weighted by the score */
 
 #ifdef __cplusplus
 extern "C" {
@@ -81,9 +83,19 @@ int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtyp
 int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave,
                cudaStream_t stream);
 int tlc_gather_rows(const float* x, const int* rows, int R, int D, float* out, cudaStream_t stream);
-/* out[T, F] = act(gate) * up as tlc_swiglu; act 0: SiLU, 1: GELU in its tanh form. */
+/* out[T, F] = act(gate) * up as tlc_swiglu; act 0: SiLU, 1: GELU in its tanh form, 2 (TLC_ACT_SWISH_CLAMPED): with
+ * g = min(gate, limit) and u = up held within +-limit, g * sigmoid(alpha g) * (u + 1). */
 int tlc_glu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave, int act,
-            cudaStream_t stream);
+            float limit, float alpha, cudaStream_t stream);
+/* out[t, :D] = x[t, :D] (act 0) or tanh(x[t, :D]) (act 1) in the given type; row strides ldx, ldo. */
+int tlc_convert(const float* x, int ldx, int T, int D, void* out, int dtype, int ldo, int act, cudaStream_t stream);
+/* x[i] = cap * tanh(x[i] / cap) for n values, in place. */
+int tlc_softcap(float* x, long long n, float cap, cudaStream_t stream);
+/* The mean of several sublayers' results, each normed by itself: y = scale * sum_p parts[t, p, :] / rms(parts[t, p, :]) *
+ * w[p, :] (parts float [T, n_parts, D], w float [n_parts, D], rms with eps inside the root); then res[t] (+)= y, or with
+ * an outer weight wo [D]: res[t] (+)= y / rms(y; eps_o) * wo. */
+int tlc_rmsnorm_mean_add(const float* parts, int n_parts, const float* w, float eps, float scale, const float* wo,
+                         float eps_o, int T, int D, float* res, int accumulate, cudaStream_t stream);
 /* RMSNorm with token shift: n[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w and out[t] = n[t] + (n[t-1] - n[t]) * mu, with
  * n[t-1] the normed row of the sequence's previous token: the row above in this step, or what the sequence's slot of
  * state [n_slots, D] holds from its last step (zeros at position 0).  The slot then receives the sequence's last normed
@@ -148,16 +160,19 @@ int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int ld, int q_of
                       const int* positions, const int* row_seq, const int* slots, const int* block_table,
                       int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream);
 /* Causal grouped-query attention of every row over its sequence's pages (keys 0..position, or the last
- * `window`); any sizes, both element types; a warp per (row, head). */
+ * `window`); any sizes, both element types; a warp per (row, head).  softcap > 0: score <- softcap * tanh(score /
+ * softcap) after the scale; sink: one more term of score 0 in the softmax's denominator, which carries no value. */
 int tlc_attention(const void* q, int dtype, const void* k_pages, const void* v_pages, const int* block_table,
                   int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
-                  int H, int KV, int hd, float scale, int window, int out_ld, cudaStream_t stream);
+                  int H, int KV, int hd, float scale, int window, int out_ld, float softcap, int sink,
+                  cudaStream_t stream);
 /* Single-token rows: keys split across blocks of 128, partial results in part_o [T, H, splits, hd] and
  * part_ml [T, H, splits, 2], then merged. */
 int tlc_attention_decode(const void* q, int dtype, const void* k_pages, const void* v_pages,
                          const int* block_table, int max_pages, const int* positions, const int* row_seq,
                          const int* slots, void* out, float* part_o, float* part_ml, int T, int H, int KV,
-                         int hd, float scale, int window, int max_keys, int out_ld, cudaStream_t stream);
+                         int hd, float scale, int window, int max_keys, int out_ld, float softcap, int sink,
+                         cudaStream_t stream);
 /* Single-token rows of a bfloat16 cache in one kernel: rotation of q and the new key, store of the new
  * K/V row, scores and outputs on the tensor cores, merge of the splits by the last block to arrive
  * (arrivals: zeroed counters, at least T*KV, back at zero afterwards). */
@@ -286,6 +301,10 @@ int tlc_mingru_scan(const float* proj, int ld, int z_off, int u_off, int g_off, 
 int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim, const float* inv_freq,
                        int rot, int interleaved, float norm_eps, const int* positions, int T, cudaStream_t stream);
 int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n, int T, int act, cudaStream_t stream);
+/* In place on the 32-bit projection: the q_n query columns from q_off, all heads together, are divided by their root mean
+ * square (eps inside the root) and multiplied by qw [q_n]; the k_n key columns from k_off likewise with kw [k_n]. */
+int tlc_qk_whole_norm(float* qkv, int ld, int q_off, int q_n, const float* qw, int k_off, int k_n, const float* kw, float eps,
+                      int T, cudaStream_t stream);
 
 /* ---- gated delta rule (delta_rule.cu) -------------------------------------------------------------------
  * Per head: M <- a M; w = b (v - M^T k); M <- M + k w^T; r = M^T q (a the decay, b the write strength `beta`), with M
@@ -307,11 +326,19 @@ int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, co
  * the picked logits (TLC_ROUTE_SOFTMAX); order [T*top] lists the pairs (t * top + k) sorted
  * by expert, offsets [E+1] every expert's first sorted position, tile_off [E+1] its first tile of tile_rows sorted rows
  * (32 for tlc_moe_gate_up / tlc_moe_down; 32 or 64 for tlc_moe_experts_mma, which is told the same number). */
-int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, int* ids, float* wts, int* order, int* offsets,
-                  int* tile_off, int tile_rows, cudaStream_t stream);
+/* TLC_ROUTE_SOFTMAX_ALL: scores s = softmax over all E outputs; chosen by s + choice_bias[e] (choice_bias NULL: by s),
+ * weighted by s.  The last n_identity of the E outputs have no expert's weights (they stand for experts that return their
+ * input, tlc_moe_identity): their pairs are sorted behind the others and get no tiles, and the expert products are called
+ * with E - n_identity experts. */
+int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, const float* choice_bias, int n_identity,
+                  int* ids, float* wts, int* order, int* offsets, int* tile_off, int tile_rows, cudaStream_t stream);
+/* y[pair, :D] = wts[pair] * x[token(pair), :D] for every pair with ids[pair] >= E. */
+int tlc_moe_identity(const void* x, int x_dtype, int ldx, const int* ids, const float* wts, int T, int top, int E, int D,
+                     float* y, cudaStream_t stream);
 /* act[i, :F] for sorted position i from g | u = wgu[e] x[token], wgu [E, 2F, D], and the pair's weight w: with w_out 0
  * the weight scales the expert's input, act(w g) * (w u); with w_out 1 its output, w * act(g, u).  act: TLC_ACT_SILU,
- * TLC_ACT_GELU_TANH, or TLC_ACT_SWISH_CLAMPED with its limit and alpha. */
+ * TLC_ACT_GELU_TANH, or TLC_ACT_SWISH_CLAMPED with its limit and alpha; TLC_ACT_RELU_SQUARED: experts without a gate,
+ * wgu [E, F, D], act = w * max(wgu[e] x, 0)^2 (one product). */
 int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_dtype, const int* order,
                     const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
                     void* act, int act_dtype, int act_code, int w_out, float limit, float alpha, cudaStream_t stream);
@@ -329,6 +356,20 @@ int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void* w, void* 
 int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, const void* wd, const int* order, const int* offsets,
                         const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
                         int tile_rows, int act_code, int w_out, float limit, float alpha, cudaStream_t stream);
+
+/* ---- time mixing with a decaying matrix state (wkv.cu) ------------------------------------------------------
+ * tlc_shift_mix: out[t, s, :] = x[t] + (x[t-1] - x[t]) * mu[s] for n_mix learned vectors mu [n_mix, D]; x[t-1] is the row
+ * above, or for a sequence's first row of the step what its slot of state [n_slots, D] holds (zeros at position 0); the
+ * slot then receives the sequence's last row.  x float [T, D]; out [T, n_mix, D] of out_dtype.
+ * tlc_wkv_scan: per (sequence, head) o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T with
+ * w_t = exp(-exp(decay_log_t)); r, k, v: columns r_off, k_off, v_off (+ h * d) of rkv float [T, ld]; decay_log float
+ * [T, ld_w] (H * d columns); bonus u float [H, d]; state float [n_slots, H, d, d] (zero at position 0, updated in
+ * place); out float [T, out_ld] (H * d columns). */
+int tlc_shift_mix(const float* x, const float* mu, int n_mix, int T, int D, const int* row_seq, const int* cu_seqlens,
+                  const int* slots, const int* start_pos, float* state, void* out, int out_dtype, cudaStream_t stream);
+int tlc_wkv_scan(const float* rkv, int ld, int r_off, int k_off, int v_off, const float* decay_log, int ld_w,
+                 const float* bonus, float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B,
+                 int H, int d, float* out, int out_ld, cudaStream_t stream);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
 /* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte

@@ -22,7 +22,7 @@ from ..parts.linear import StackedLinear, matrix_dtype
 class Model:
     def __init__(self, config, layer_specs: Sequence[LayerSpec], schedule: Optional[Sequence[LayerRun]],
                  final_norm: PartSpec, embed_name: str, head_name: Optional[str], vocab: int, hidden: int,
-                 embed_scale: float = 1.0, head_scale: float = 1.0):
+                 embed_scale: float = 1.0, head_scale: float = 1.0, logit_softcap: float = 0.0):
         self.config = config
         self.vocab, self.hidden = int(vocab), int(hidden)
         self.layers: List[Block] = [Block(s) for s in layer_specs]
@@ -56,6 +56,7 @@ class Model:
         self.final_norm = final_norm.build()
         self.embed_name, self.head_name = embed_name, head_name            # head_name None: tied (core.c:1246-1249)
         self.embed_scale = float(embed_scale)
+        self.logit_softcap = float(logit_softcap)          # > 0: logits <- cap * tanh(logits / cap)
         self.head = StackedLinear(hidden)
         self.head.add(head_name or embed_name, vocab, None, 1.0, head_scale)
         self.embed_table: Optional[torch.Tensor] = None
@@ -76,6 +77,14 @@ class Model:
                 seen.add(s.name)
                 out.append(s)
         return out
+
+    def adopt_shapes(self, shapes: Dict[str, tuple]) -> None:
+        """Before the tensors are checked: a part with a size that no configuration key gives (shapes_from) reads it off
+        the stored tensors' shapes."""
+        for layer in self.layers:
+            for part in layer.parts():
+                if hasattr(part, "shapes_from"):
+                    part.shapes_from(shapes)
 
     def cache_requests(self) -> Dict[int, list]:
         """Cache needs per entry of the run order that owns a cache (key: its index)."""
@@ -121,4 +130,6 @@ class Model:
         self.final_norm.forward(x, normed, want_rows)
         logits = torch.empty((n, self.vocab), dtype=torch.float32, device=self.device)
         self.head.forward(normed, logits)
+        if self.logit_softcap > 0:
+            ops.softcap(logits, self.logit_softcap)
         return logits

@@ -65,9 +65,9 @@ _SIGNATURES = {
     "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                _i, _i, _vp]),
-    "tlc_attention": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp]),
+    "tlc_attention": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _f, _i, _vp]),
     "tlc_attention_decode": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
-                                  _i, _vp]),
+                                  _i, _f, _i, _vp]),
     "tlc_attention_decode_fused_ok": (_i, [_i, _i, _i]),
     "tlc_attention_decode_fused_passes": (_i, [_i]),
     "tlc_attention_decode_fused": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp,
@@ -91,7 +91,14 @@ _SIGNATURES = {
     "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
     "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                               _i, _i, _vp, _vp]),
-    "tlc_glu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp]),
+    "tlc_glu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),
+    "tlc_convert": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp]),
+    "tlc_softcap": (_i, [_vp, _ll, _f, _vp]),
+    "tlc_rmsnorm_mean_add": (_i, [_vp, _i, _vp, _f, _f, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_qk_whole_norm": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _f, _i, _vp]),
+    "tlc_shift_mix": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "tlc_wkv_scan": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_moe_identity": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "tlc_rmsnorm_shift": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "tlc_rmsnorm_add": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _f, _i, _i, _vp, _i, _vp]),
     "tlc_latent_prepare": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i,
@@ -107,7 +114,7 @@ _SIGNATURES = {
     "tlc_linear_heads_mma": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _f, _f, _vp]),
     "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
-    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),
     "tlc_qk_rotate_norm": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _f, _vp, _i, _vp]),
     "tlc_gate_mul": (_i, [_vp, _i, _i, _vp, _i, _i, _i, _i, _vp]),
@@ -305,21 +312,58 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) 
 
 
 GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+DENSE_ACTS = dict(GLU_ACTS, swish_clamped=2)       # the clamped swish has no fused product epilogue: product, then glu()
 
 
-def glu(gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu", interleaved: bool = False) -> None:
-    """out = act(gate) * up with gate | up laid out as for swiglu; act: "silu" or "gelu_tanh"."""
+def glu(gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu", interleaved: bool = False, limit: float = 0.0,
+        alpha: float = 1.0) -> None:
+    """out = act(gate) * up with gate | up laid out as for swiglu; act: "silu", "gelu_tanh", or "swish_clamped": with
+    g = min(gate, limit) and u = up held within +-limit, g * sigmoid(alpha * g) * (u + 1)."""
     _gpu(gate_up, out)
     T, F2 = gate_up.shape
     F = F2 // 2
-    if act not in GLU_ACTS:
+    if act not in DENSE_ACTS:
         raise KernelError(f"glu: unknown activation '{act}'; known: {sorted(GLU_ACTS)}")
     if not out.is_contiguous() or tuple(out.shape) != (T, F) or F2 != 2 * F:
         raise KernelError("glu: out must be contiguous [T, F]")
     if interleaved and F % 8:
         raise KernelError("glu: the interleaved layout needs a multiple of 8 features")
     _call("tlc_glu", gate_up.data_ptr(), dtype_code(gate_up.dtype), _rows(gate_up, "gate_up"), F, T,
-          out.data_ptr(), dtype_code(out.dtype), int(bool(interleaved)), GLU_ACTS[act], _stream())
+          out.data_ptr(), dtype_code(out.dtype), int(bool(interleaved)), DENSE_ACTS[act], float(limit), float(alpha), _stream())
+
+
+def convert(x: torch.Tensor, out: torch.Tensor, act: str = "none") -> None:
+    """out = x (float32 [T, D], dense rows) in out's type, or with act "tanh" its tanh; out may be a range of the columns
+    of a wider buffer."""
+    _gpu(x, out)
+    T, D = x.shape
+    if x.dtype != torch.float32 or act not in ("none", "tanh"):
+        raise KernelError("convert: a float32 input; act 'none' or 'tanh'")
+    _call("tlc_convert", x.data_ptr(), _rows(x, "convert input"), T, D, out.data_ptr(), dtype_code(out.dtype),
+          _out_rows(out, T, D, "convert"), int(act == "tanh"), _stream())
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap), in place on a contiguous float32 tensor."""
+    _gpu(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("softcap: a contiguous float32 tensor")
+    _call("tlc_softcap", x.data_ptr(), x.numel(), float(cap), _stream())
+
+
+def rmsnorm_mean_add(parts: torch.Tensor, weights: torch.Tensor, eps: float, scale: float, residual: torch.Tensor,
+                     outer_weight: Optional[torch.Tensor] = None, outer_eps: float = 0.0, accumulate: bool = True) -> None:
+    """y = scale * sum_p rmsnorm(parts[:, p, :]) * weights[p]  (parts float32 [T, n, D], weights float32 [n, D]); then
+    residual (+)= y, or with an outer weight [D] residual (+)= rmsnorm(y; outer_eps) * outer_weight."""
+    _gpu(parts, weights, residual, outer_weight)
+    T, n, D = parts.shape
+    if parts.dtype != torch.float32 or not parts.is_contiguous() or residual.dtype != torch.float32 \
+            or not residual.is_contiguous() or tuple(residual.shape) != (T, D):
+        raise KernelError("rmsnorm_mean_add: parts float32 [T, n, D] and residual float32 [T, D], contiguous")
+    _f32vec(weights, n * D, "rmsnorm_mean_add weights")
+    _f32vec(outer_weight, D, "rmsnorm_mean_add outer weight")
+    _call("tlc_rmsnorm_mean_add", parts.data_ptr(), n, weights.data_ptr(), float(eps), float(scale), _p(outer_weight),
+          float(outer_eps), T, D, residual.data_ptr(), int(bool(accumulate)), _stream())
 
 
 def rmsnorm_shift(x: torch.Tensor, weight: torch.Tensor, mix: torch.Tensor, eps: float, state: torch.Tensor, step,
@@ -531,7 +575,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
               hd: int, scale: float, window: int = 0, decode_max_keys: int = 0,
               cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None,
-              max_keys: int = 0, max_blocks: int = 0, key_ranges: int = 0) -> None:
+              max_keys: int = 0, max_blocks: int = 0, key_ranges: int = 0, softcap: float = 0.0, sink: bool = False) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
     or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
     steps of sequences no longer than that: keys are then split across blocks.  With
@@ -540,7 +584,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     after this step) it cuts the key range of long rows into pieces that run side by side.  max_blocks > 0
     bounds how many blocks (hence SMs) the tensor-core kernel of prompts holds at a time, for a caller that runs
     other kernels beside it; the result does not depend on it.  key_ranges > 0 fixes into how many ranges that
-    kernel cuts the keys of a row tile (0: chosen: more than one for few rows over many keys)."""
+    kernel cuts the keys of a row tile (0: chosen: more than one for few rows over many keys).  softcap > 0: scores are
+    softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one more term of score 0, which
+    carries no value (both served by the warp kernels and the split-key kernels of single tokens)."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.dtype != q.dtype or k_pages.dtype != q.dtype:
@@ -553,9 +599,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_decode", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(),
               slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
-              int(window or 0), int(decode_max_keys), out_ld, _stream())
+              int(window or 0), int(decode_max_keys), out_ld, float(softcap), int(bool(sink)), _stream())
         return
-    tiled = decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
+    tiled = not (softcap > 0 or sink) and decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
         and hd in (64, 128) and not DISABLE_TILED_ATTENTION
     if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
             and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
@@ -588,7 +634,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         return
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),
-          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), out_ld, _stream())
+          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), out_ld, float(softcap), int(bool(sink)), _stream())
 
 
 DISABLE_FUSED_DECODE_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_FUSED_DECODE_ATTENTION", "0")))
@@ -963,28 +1009,33 @@ def mingru_scan(proj: torch.Tensor, z_off: int, u_off: int, g_off: int, width: i
 
 
 # ---- mixture of experts ------------------------------------------------------------------------------------
-def _moe_mma_ok(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype) -> bool:
-    D, F = w_gate_up.shape[2], w_gate_up.shape[1] // 2
+def _moe_mma_ok(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype, F: Optional[int] = None) -> bool:
+    D = w_gate_up.shape[2]
+    F = w_gate_up.shape[1] // 2 if F is None else F
     return bool(_grouped_mma and act_dtype == torch.bfloat16 and F % 8 == 0 and D % 8 == 0
                 and library().tlc_grouped_mma_ok(dtype_code(x.dtype), dtype_code(w_gate_up.dtype), x.data_ptr(), _rows(x, "moe input"),
                                                  0, w_gate_up.data_ptr(), D))
 
 
-def moe_tile_rows(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype, top: int) -> int:
+def moe_tile_rows(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype, top: int, F: Optional[int] = None) -> int:
     """Rows of a tile of the experts' products for this input: 64 where the tensor-core kernel runs and an expert gets
     64 rows or more on average, else 32.  The routing is made for that number (moe_route) and carries it."""
     E = w_gate_up.shape[0]
-    return 64 if _moe_mma_ok(x, w_gate_up, act_dtype) and x.shape[0] * top >= 64 * E else 32
+    return 64 if _moe_mma_ok(x, w_gate_up, act_dtype, F) and x.shape[0] * top >= 64 * E else 32
 
 
-ROUTE_WEIGHTS = {"sigmoid": 0, "softmax": 1}
-MOE_ACTS = dict(GLU_ACTS, swish_clamped=2)
+ROUTE_WEIGHTS = {"sigmoid": 0, "softmax": 1, "softmax_all": 2}
+MOE_ACTS = dict(GLU_ACTS, swish_clamped=2, relu_squared=3)
+UNGATED_ACTS = ("relu_squared",)          # experts of one product: w_up [E, F, D], no gate
 
 
-def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32, weights: str = "sigmoid"):
+def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32, weights: str = "sigmoid",
+              choice_bias: Optional[torch.Tensor] = None, n_identity: int = 0):
     """Routing of every row of logits (float32 [T, >= E], the first E columns): returns (ids [T*top] int32, weights
     [T*top] float32 = sigmoid of the chosen logits, or with weights "softmax" a softmax restricted to the picked logits,
-    order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as tlc_moe_route describes them."""
+    order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as tlc_moe_route describes them.  With weights "softmax_all"
+    the scores are the softmax over all n_experts outputs, an expert is chosen by score + choice_bias and weighted by its
+    score.  The last n_identity of the n_experts outputs have no weights of an expert: no tile covers their pairs."""
     if weights not in ROUTE_WEIGHTS:
         raise KernelError(f"moe_route: unknown weighting '{weights}'; known: {sorted(ROUTE_WEIGHTS)}")
     _gpu(logits)
@@ -999,8 +1050,10 @@ def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 3
     wts = torch.empty(T * top, dtype=torch.float32, device=dev)
     global _launches
     _launches += 1                      # (two kernels)
+    _f32vec(choice_bias, n_experts, "moe_route choice bias")
+    _gpu(choice_bias)
     _call("tlc_moe_route", logits.data_ptr(), _rows(logits, "router logits"), T, int(n_experts), int(top), ROUTE_WEIGHTS[weights],
-          ids.data_ptr(),
+          _p(choice_bias), int(n_identity), ids.data_ptr(),
           wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), int(tile_rows), _stream())
     return ids, wts, order, offsets, tile_off, int(tile_rows)
 
@@ -1018,7 +1071,7 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     ids, wts, order, offsets, tile_off, tile_rows = routing
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
-    F = F2 // 2
+    F = F2 if act_fn in UNGATED_ACTS else F2 // 2         # (experts without a gate: w_gate_up is [E, F, D])
     if not w_gate_up.is_contiguous() or not w_down.is_contiguous() or tuple(w_down.shape) != (E, D, F) \
             or w_gate_up.shape[2] != D or w_gate_up.dtype != w_down.dtype:
         raise KernelError("moe_experts: w_gate_up [E, 2F, D] and w_down [E, D, F] contiguous and of one type")
@@ -1026,7 +1079,7 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
             or y.numel() != T * top * D:
         raise KernelError("moe_experts: act [T*top, F] contiguous, y contiguous float32 [T, top, D]")
     ldx = _rows(x, "moe input")
-    if _moe_mma_ok(x, w_gate_up, act.dtype):
+    if _moe_mma_ok(x, w_gate_up, act.dtype, F):
         _call("tlc_moe_experts_mma", x.data_ptr(), ldx, w_gate_up.data_ptr(), w_down.data_ptr(), order.data_ptr(), offsets.data_ptr(),
               tile_off.data_ptr(), wts.data_ptr(), T, E, int(top), F, D, act.data_ptr(), y.data_ptr(), tile_rows, code, w_out,
               float(limit), float(alpha), _stream())
@@ -1038,6 +1091,70 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
           F, D, act.data_ptr(), dtype_code(act.dtype), code, w_out, float(limit), float(alpha), _stream())
     _call("tlc_moe_down", act.data_ptr(), dtype_code(act.dtype), w_down.data_ptr(), dtype_code(w_down.dtype), order.data_ptr(),
           offsets.data_ptr(), tile_off.data_ptr(), T, E, int(top), F, D, y.data_ptr(), _stream())
+
+
+def moe_identity(x: torch.Tensor, routing, top: int, n_experts: int, y: torch.Tensor) -> None:
+    """y[t, k, :] = weight * x[t] for every pair that the routing sent to a router output >= n_experts (an expert that
+    returns its input); x float32 or the activation type, y float32 [T, top, D]."""
+    _gpu(x, y)
+    ids, wts = routing[0], routing[1]
+    T, D = x.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or y.numel() != T * top * D:
+        raise KernelError("moe_identity: y contiguous float32 [T, top, D]")
+    _call("tlc_moe_identity", x.data_ptr(), dtype_code(x.dtype), _rows(x, "moe input"), ids.data_ptr(), wts.data_ptr(), T, int(top),
+          int(n_experts), D, y.data_ptr(), _stream())
+
+
+def qk_whole_norm(qkv: torch.Tensor, q_off: int, q_n: int, q_weight: torch.Tensor, k_off: int, k_n: int, k_weight: torch.Tensor,
+                  eps: float) -> None:
+    """In place on the float32 projection: its q_n query columns from q_off (all heads together) become
+    q / sqrt(mean(q^2) + eps) * q_weight, its k_n key columns from k_off likewise."""
+    _gpu(qkv, q_weight, k_weight)
+    ld = _rows(qkv, "qkv")
+    if qkv.dtype != torch.float32 or max(q_off + q_n, k_off + k_n) > max(ld, qkv.shape[1]):
+        raise KernelError("qk_whole_norm: a float32 projection that holds the queries and keys")
+    _f32vec(q_weight, q_n, "query norm weight")
+    _f32vec(k_weight, k_n, "key norm weight")
+    _call("tlc_qk_whole_norm", qkv.data_ptr(), ld, int(q_off), int(q_n), q_weight.data_ptr(), int(k_off), int(k_n),
+          k_weight.data_ptr(), float(eps), qkv.shape[0], _stream())
+
+
+# ---- time mixing with a decaying matrix state -------------------------------------------------------------------
+MAX_WKV_HEAD_DIM = 256    # wkv.cu: 8 lanes a column x 32 rows a lane
+
+
+def shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor) -> None:
+    """out[t, s] = x[t] + (x[t-1] - x[t]) * mu[s]: x float32 [T, D] contiguous, mu float32 [n, D], out [T, n, D]; x[t-1] is
+    the row above or, for a sequence's first row of the step, its slot's row of state [n_slots, D] (zeros at position 0),
+    which then receives the sequence's last row."""
+    _gpu(x, mu, state, out)
+    T, D = x.shape
+    n = mu.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or state.dtype != torch.float32 or not state.is_contiguous() \
+            or state.shape[-1] != D or not out.is_contiguous() or tuple(out.shape) != (T, n, D):
+        raise KernelError("shift_mix: x float32 [T, D], state float32 [n_slots, D], out [T, n, D], all contiguous")
+    _f32vec(mu, n * D, "shift_mix mu")
+    _call("tlc_shift_mix", x.data_ptr(), mu.data_ptr(), n, T, D, step.row_seq.data_ptr(), step.cu_seqlens.data_ptr(),
+          step.slots.data_ptr(), step.start_pos.data_ptr(), state.data_ptr(), out.data_ptr(), dtype_code(out.dtype), _stream())
+
+
+def wkv_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, decay_log: torch.Tensor, bonus: torch.Tensor,
+             state: torch.Tensor, step, H: int, d: int, out: torch.Tensor) -> None:
+    """Per (sequence, head): o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(exp(-exp(decay_log_t))) S + k_t v_t^T.
+    rkv float32 [T, *] holds r, k, v from their column offsets (H * d each); decay_log float32 [T, H*d]; bonus u float32
+    [H, d]; state float32 [n_slots, H, d, d] (zero at position 0; updated in place); out float32 [T, H*d]."""
+    _gpu(rkv, decay_log, bonus, state, out)
+    T = rkv.shape[0]
+    if rkv.dtype != torch.float32 or decay_log.dtype != torch.float32 or out.dtype != torch.float32 \
+            or state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, d, d):
+        raise KernelError("wkv_scan: float32 projections and a contiguous float32 state [n_slots, H, d, d]")
+    _f32vec(bonus, H * d, "wkv bonus")
+    ld = _rows(rkv, "wkv projections")
+    if max(r_off, k_off, v_off) + H * d > max(ld, rkv.shape[1]) or decay_log.shape[1] != H * d:
+        raise KernelError("wkv_scan: r, k or v lies outside the projection's row, or the decay has another width")
+    _call("tlc_wkv_scan", rkv.data_ptr(), ld, int(r_off), int(k_off), int(v_off), decay_log.data_ptr(), _rows(decay_log, "wkv decay"),
+          bonus.data_ptr(), state.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(),
+          step.n_seqs, int(H), int(d), out.data_ptr(), _out_rows(out, T, H * d, "wkv_scan"), _stream())
 
 
 # ---- queries, keys and output gate of an attention mixer ---------------------------------------------------

@@ -202,13 +202,16 @@ class LayerSpec:
     add into the residual stream, pre-feed-forward norm, feed-forward.  With an output norm a sublayer's result is
     normed before it is added: x <- x + out_norm(sublayer(norm(x))).  A norm part that keeps per-sequence state (a token
     shift) declares it like a mixer does.  A feed-forward without a norm of its own (ffn_norm None) runs in parallel with
-    the mixers: it reads what the mixers read, h = mixer_norm(x), and x <- x + mixers(h) + ffn(h)."""
+    the mixers: it reads what the mixers read, h = mixer_norm(x), and x <- x + mixers(h) + ffn(h).  A norm named "none"
+    in front of a sublayer means that it reads the stream itself.  mixer_join (a norm part with add_joined, "rmsnorm_mean")
+    says how several mixers' results become one where that is not their sum: x <- x + out_norm(join(mixer_i(h)))."""
     mixer_norm: PartSpec
     mixers: Tuple[PartSpec, ...]
     ffn_norm: Optional[PartSpec]
     ffn: Optional[PartSpec]
     mixer_out_norm: Optional[PartSpec] = None
     ffn_out_norm: Optional[PartSpec] = None
+    mixer_join: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

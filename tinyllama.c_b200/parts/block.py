@@ -77,6 +77,10 @@ class Block(Part):
         self.ffn = spec.ffn.build() if spec.ffn is not None else None
         self.mixer_out_norm = spec.mixer_out_norm.build() if spec.mixer_out_norm is not None else None
         self.ffn_out_norm = spec.ffn_out_norm.build() if spec.ffn_out_norm is not None else None
+        # how the mixers' results are joined where that is not their sum (each normed by itself, then averaged)
+        self.mixer_join = spec.mixer_join.build() if spec.mixer_join is not None else None
+        if self.mixer_join is not None and not self.mixers:
+            raise ValueError("a join of the mixers' results needs mixers")
         # a feed-forward without a norm of its own is a parallel branch: it reads the mixers' normed input
         self.parallel_ffn = self.ffn is not None and self.ffn_norm is None
         if self.parallel_ffn and (not self.mixers or self.ffn_out_norm is not None or self.mixer_out_norm is not None):
@@ -89,8 +93,8 @@ class Block(Part):
         self._ffn_overwrites = takes(self.ffn)
 
     def parts(self) -> List[Part]:
-        return [p for p in [self.mixer_norm, *self.mixers, self.mixer_out_norm, self.ffn_norm, self.ffn, self.ffn_out_norm]
-                if p is not None]
+        return [p for p in [self.mixer_norm, *self.mixers, self.mixer_join, self.mixer_out_norm, self.ffn_norm, self.ffn,
+                            self.ffn_out_norm] if p is not None]
 
     def weight_specs(self) -> List[WeightSpec]:
         return [s for p in self.parts() for s in p.weight_specs()]
@@ -109,7 +113,8 @@ class Block(Part):
         # share one product: their input projections are stacked.  Any other mixer gets the normed
         # input as a tensor.
         self.fused_in, self.fused_offsets = None, []
-        if len(self.mixers) > 1 and self.mixer_out_norm is None and all(hasattr(m, "input_projection") and hasattr(m, "forward_projected")
+        if len(self.mixers) > 1 and (self.mixer_out_norm is None or self.mixer_join is not None) \
+                and all(hasattr(m, "input_projection") and hasattr(m, "forward_projected")
                                         for m in self.mixers):
             projs = [m.input_projection() for m in self.mixers]
             self.fused_in = StackedLinear.fuse_bound(projs)
@@ -121,7 +126,7 @@ class Block(Part):
         # write side by side into one buffer, and one product over the weights side by side along K forms
         # the sum in its accumulator.
         self.fused_out, self.out_offsets, self.out_scales = None, [], []
-        if self.fused_in is not None and FUSE_OUTPUTS and all(hasattr(m, "output_projection") and hasattr(m, "mix")
+        if self.fused_in is not None and self.mixer_join is None and FUSE_OUTPUTS and all(hasattr(m, "output_projection") and hasattr(m, "mix")
                                                               for m in self.mixers):
             outs = [m.output_projection() for m in self.mixers]
             fused = StackedLinear.fuse_bound_inputs(outs, [bool(getattr(m, "mix_takes_scale", False)) for m in self.mixers])
@@ -132,11 +137,12 @@ class Block(Part):
                     self.out_offsets.append((off, pr.in_features))
                     off += pr.in_features
 
-    def _mix_in_parallel(self, parts, step: StepInfo, cache: LayerCache, x32: torch.Tensor) -> None:
+    def _mix_in_parallel(self, parts, step: StepInfo, cache: LayerCache, x32: torch.Tensor, outs: Optional[torch.Tensor] = None) -> None:
         """One mixer runs on the current stream, every other on a side stream that starts after the
         shared input projection.  Output projections add into the residual stream one after the
         other on the current stream, in the mixers' order, each after its mixer has finished.  (Under stream capture the
-        side streams become parallel branches of the graph.)"""
+        side streams become parallel branches of the graph.)  outs [T, n, D]: every mixer's output projection is written
+        to its own rows outs[:, i] instead (a layer that joins its mixers' results by something else than their sum)."""
         main = _current_stream(x32.device)
         if not hasattr(self, "_side"):
             self._side = [torch.cuda.Stream(device=x32.device) for _ in self.mixers[1:]]
@@ -181,7 +187,9 @@ class Block(Part):
         acts[here] = self._mix(here, parts[here], step, cache, views[here], join if early else None)
         join()
         for i, m in enumerate(self.mixers):          # outputs in the mixers' order, whatever ran where
-            if joint is None:
+            if outs is not None:
+                m.output_projection().forward(acts[i], outs[:, i], accumulate=False)
+            elif joint is None:
                 m.output(acts[i], x32)
         if joint is not None:
             self.fused_out.forward(joint, x32, accumulate=True)
@@ -242,6 +250,30 @@ class Block(Part):
         main.wait_event(self._ffn_done)
         self.ffn.add_parts(terms, x32)
 
+    def _joined_mixers(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
+        """x <- x + out_norm(join(mixer_i(h))): every mixer's result in rows of its own, then the join (and the norm after
+        it) in one kernel.  Mixers that offer their projections share the input product and, in one-token steps, run side
+        by side on streams."""
+        reads = [bool(getattr(m, "reads_stream", False)) and getattr(self.mixer_norm, "identity", False) for m in self.mixers]
+        normed = None if all(reads) else self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
+        T, n = x32.shape[0], len(self.mixers)
+        outs = scratch_buf("block.joined", (T, n, x32.shape[1]), torch.float32, x32.device)
+        if self.fused_in is not None and all(hasattr(m, "mix") and hasattr(m, "output_projection") for m in self.mixers):
+            proj = scratch_buf("block.proj", (T, self.fused_in.out_features), torch.float32, x32.device)
+            self.fused_in.forward(normed, proj)
+            parts = [proj[:, off:off + w] for off, w in self.fused_offsets]
+            if (step.max_new == 1 or PARALLEL_PROMPT_MIXERS) and x32.is_cuda and PARALLEL_MIXERS:
+                self._mix_in_parallel(parts, step, cache, x32, outs)
+            else:
+                for i, (m, part) in enumerate(zip(self.mixers, parts)):
+                    m.output_projection().forward(m.mix(part, step, cache), outs[:, i], accumulate=False)
+        else:
+            for i, m in enumerate(self.mixers):
+                if not self._mixer_overwrites[i]:
+                    raise ValueError("a layer that joins its mixers' results needs mixers whose forward() can overwrite its target")
+                m.forward(x32 if reads[i] else normed, step, cache, outs[:, i], accumulate=False)
+        self.mixer_join.add_joined(outs, x32, self.mixer_out_norm)
+
     def _pre_norm(self, norm, x32: torch.Tensor, tag: str, step: StepInfo, cache: LayerCache) -> torch.Tensor:
         normed = scratch_buf(tag, x32.shape, self.dtype, x32.device)
         if hasattr(norm, "forward_step"):             # a norm with per-sequence state (token shift)
@@ -252,17 +284,20 @@ class Block(Part):
 
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""
-        if self.mixers and self.mixer_out_norm is not None:
-            # x <- x + out_norm(sum of the mixers' outputs)
-            normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
+        if self.mixers and self.mixer_join is not None:
+            self._joined_mixers(x32, step, cache)
+        elif self.mixers and self.mixer_out_norm is not None:
+            # x <- x + out_norm(sum of the mixers' outputs); a mixer that reads the stream itself gets the 32-bit rows
+            reads = [bool(getattr(m, "reads_stream", False)) and getattr(self.mixer_norm, "identity", False) for m in self.mixers]
+            normed = None if all(reads) else self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
             y = scratch_buf("block.mixed", x32.shape, torch.float32, x32.device)
             if not self._mixer_overwrites[0]:
                 y.zero_()
             for i, m in enumerate(self.mixers):
                 if self._mixer_overwrites[i]:
-                    m.forward(normed, step, cache, y, accumulate=i > 0)
+                    m.forward(x32 if reads[i] else normed, step, cache, y, accumulate=i > 0)
                 else:
-                    m.forward(normed, step, cache, y)
+                    m.forward(x32 if reads[i] else normed, step, cache, y)
             self.mixer_out_norm.add_normed(y, x32)
         elif self.mixers:
             normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
@@ -299,11 +334,13 @@ class Block(Part):
     def _feed_forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """A feed-forward with a norm of its own, after the mixers."""
         normed = self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache)
+        # without a norm in front, a feed-forward that can use them (takes_stream) also gets the 32-bit rows themselves
+        more = {"stream": x32} if getattr(self.ffn_norm, "identity", False) and getattr(self.ffn, "takes_stream", False) else {}
         if self.ffn_out_norm is None:
-            self.ffn.forward(normed, x32)
+            self.ffn.forward(normed, x32, **more)
         elif hasattr(self.ffn, "forward_parts"):
             # a feed-forward whose result is a sum of terms hands them to the norm, which adds them up itself
-            parts, extra, gate = self.ffn.forward_parts(normed)
+            parts, extra, gate = self.ffn.forward_parts(normed, **more)
             self.ffn_out_norm.add_normed(parts, x32, extra, gate)
         else:
             y = scratch_buf("block.ffn_out", x32.shape, torch.float32, x32.device)

@@ -20,14 +20,18 @@ from .linear import StackedLinear
 @register_feed_forward("swiglu")
 class SwiGLU(Part):
     def __init__(self, hidden: int, intermediate: int, prefix: str, bias: bool = False, gate_scale: float = 1.0,
-                 down_scale: float = 1.0, act: str = "silu", names: Optional[Dict[str, str]] = None):
-        """act: "silu" or "gelu_tanh".  names: tensor names of gate, up, down after the prefix (default: the
+                 down_scale: float = 1.0, act: str = "silu", names: Optional[Dict[str, str]] = None, limit: float = 0.0,
+                 alpha: float = 1.0):
+        """act: "silu", "gelu_tanh", or "swish_clamped": with g = min(W_gate h, limit) and u = W_up h held within +-limit,
+        g * sigmoid(alpha g) * (u + 1) (the product and the activation are then two kernels).  names: tensor names of gate, up, down after the prefix (default: the
         gate_proj.weight / up_proj.weight / down_proj.weight of the architecture's checkpoints; biases, where asked
         for, are those names with .bias for .weight)."""
         self.hidden, self.F = int(hidden), int(intermediate)
-        if act not in ops.GLU_ACTS:
-            raise ValueError(f"feed-forward: unknown activation '{act}'; known: {sorted(ops.GLU_ACTS)}")
-        self.act = act
+        if act not in ops.DENSE_ACTS:
+            raise ValueError(f"feed-forward: unknown activation '{act}'; known: {sorted(ops.DENSE_ACTS)}")
+        if act == "swish_clamped" and not limit > 0:
+            raise ValueError(f"feed-forward: the clamped activation needs a positive limit, got {limit!r}")
+        self.act, self.limit, self.alpha = act, float(limit), float(alpha)
         nm = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
         nm.update(names or {})
         w = lambda n: prefix + nm[n]
@@ -47,7 +51,7 @@ class SwiGLU(Part):
         self.down.bind(tensors, dtype, device)
         # Rows regrouped as 8 gate rows followed by their 8 up rows, so that the product's epilogue
         # has a feature's gate and up side by side and writes silu(gate) * up directly.
-        self.interleaved = self.F % 8 == 0
+        self.interleaved = self.F % 8 == 0 and self.act in ops.GLU_ACTS
         if self.interleaved:
             F = self.F
             idx = torch.arange(2 * F, device=self.gate_up.weight.device).reshape(2, F // 8, 8).permute(1, 0, 2).reshape(-1)
@@ -66,7 +70,7 @@ class SwiGLU(Part):
         else:
             gu = scratch_buf("swiglu.gate_up", (T, 2 * self.F), torch.float32, normed.device)
             self.gate_up.forward(normed, gu)
-            ops.glu(gu, act, self.act, interleaved=self.interleaved)
+            ops.glu(gu, act, self.act, interleaved=self.interleaved, limit=self.limit, alpha=self.alpha)
         self.down.forward(act, residual, accumulate=accumulate)
 
 
@@ -90,11 +94,16 @@ class MoEFeedForward(Part):
     a softmax restricted to the picked logits (weights="softmax"); the weight applied to what the expert returns instead of
     to what it is fed (weight_on="output": sum_e s_e expert_e(h); the down product is linear, so the weight multiplies the
     32-bit activation); the activation act="swish_clamped": with g = min(W_gate h, limit) and u = W_up h held within
-    +-limit, g * sigmoid(alpha g) * (u + 1)."""
+    +-limit, g * sigmoid(alpha g) * (u + 1).  weights="softmax_all": the scores are the softmax over ALL router outputs, an
+    expert is chosen by its score plus a learned correction (choice_bias_name) and weighted by the score alone, not
+    renormalised.  n_identity > 0: the router has that many more outputs than there are experts; the last n_identity stand for
+    experts that return their input (times the weight) and have no tensors.  act="relu_squared": experts without a gate,
+    W_down max(W_up h, 0)^2 (expert_names gives up and down only; the weight goes on the output)."""
 
     def __init__(self, hidden: int, n_experts: int, top: int, expert_ff: int, router_name: str, expert_names: Dict[str, str],
                  shared: Optional[PartSpec] = None, shared_gate_name: Optional[str] = None, router_bias_name: Optional[str] = None,
-                 weights: str = "sigmoid", weight_on: str = "input", act: str = "silu", limit: float = 0.0, alpha: float = 1.0):
+                 weights: str = "sigmoid", weight_on: str = "input", act: str = "silu", limit: float = 0.0, alpha: float = 1.0,
+                 choice_bias_name: Optional[str] = None, n_identity: int = 0):
         """expert_names: patterns of gate, up, down with {e} for the expert's index."""
         if weights not in ops.ROUTE_WEIGHTS or weight_on not in ("input", "output") or act not in ops.MOE_ACTS:
             raise ValueError(f"moe: unknown weighting '{weights}', weight placement '{weight_on}' or activation '{act}'")
@@ -103,8 +112,16 @@ class MoEFeedForward(Part):
         self.router_bias_name, self.weights, self.weight_on, self.act = router_bias_name, weights, weight_on, act
         self.limit, self.alpha = float(limit), float(alpha)
         self.hidden, self.E, self.top, self.F = int(hidden), int(n_experts), int(top), int(expert_ff)
-        if not (1 <= self.top <= self.E):
-            raise ValueError(f"moe: {self.top} of {self.E} experts cannot be chosen")
+        self.n_identity, self.choice_bias_name = int(n_identity), choice_bias_name
+        self.n_out = self.E + self.n_identity              # router outputs
+        self.gated = act not in ops.UNGATED_ACTS
+        if not self.gated and weight_on != "output":
+            raise ValueError("moe: an expert without a gate is not linear before its activation: the weight goes on its output")
+        if self.n_identity < 0 or (choice_bias_name is not None and weights != "softmax_all") or (self.n_identity and shared is not None):
+            raise ValueError("moe: identity outputs cannot be negative, a choice bias belongs to weights 'softmax_all', and identity "
+                             "outputs do not go with a shared expert")
+        if not (1 <= self.top <= self.n_out):
+            raise ValueError(f"moe: {self.top} of {self.n_out} router outputs cannot be chosen")
         self.router_name, self.expert_names, self.shared_gate_name = router_name, dict(expert_names), shared_gate_name
         self.shared = shared.build() if shared is not None else None
         if (self.shared is None) != (shared_gate_name is None):
@@ -112,13 +129,16 @@ class MoEFeedForward(Part):
         self.dtype = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        specs = [WeightSpec(self.router_name, (self.E, self.hidden))]
+        specs = [WeightSpec(self.router_name, (self.n_out, self.hidden))]
         if self.router_bias_name:
-            specs.append(WeightSpec(self.router_bias_name, (self.E,)))
+            specs.append(WeightSpec(self.router_bias_name, (self.n_out,)))
+        if self.choice_bias_name:
+            specs.append(WeightSpec(self.choice_bias_name, (self.n_out,), "near_zero"))
         for e in range(self.E):
             n = {k: v.format(e=e) for k, v in self.expert_names.items()}
-            specs += [WeightSpec(n["gate"], (self.F, self.hidden)), WeightSpec(n["up"], (self.F, self.hidden)),
-                      WeightSpec(n["down"], (self.hidden, self.F))]
+            if self.gated:
+                specs.append(WeightSpec(n["gate"], (self.F, self.hidden)))
+            specs += [WeightSpec(n["up"], (self.F, self.hidden)), WeightSpec(n["down"], (self.hidden, self.F))]
         if self.shared is not None:
             specs += self.shared.weight_specs() + [WeightSpec(self.shared_gate_name, (1, self.hidden))]
         return specs
@@ -135,37 +155,47 @@ class MoEFeedForward(Part):
         self.router_bias = None
         if self.router_bias_name:                # added to the 32-bit logits in the product's epilogue (nothing on the shared gate's)
             self.router_bias = torch.zeros(self.router.shape[0], dtype=torch.float32, device=device)
-            self.router_bias[:self.E] = tensors[self.router_bias_name].to(device=device, dtype=torch.float32)
+            self.router_bias[:self.n_out] = tensors[self.router_bias_name].to(device=device, dtype=torch.float32)
+        self.choice_bias = tensors[self.choice_bias_name].to(device=device, dtype=torch.float32).contiguous() \
+            if self.choice_bias_name else None
         names = [{k: v.format(e=e) for k, v in self.expert_names.items()} for e in range(self.E)]
         mdt = torch.bfloat16
         for n in names:
-            for k in ("gate", "up", "down"):
+            for k in (("gate", "up", "down") if self.gated else ("up", "down")):
                 if matrix_dtype(tensors[n[k]].dtype, dtype) == torch.float32:
                     mdt = torch.float32
         to = lambda t: t.to(device=device, dtype=mdt)
-        self.w_gate_up = torch.stack([torch.cat([to(tensors[n["gate"]]), to(tensors[n["up"]])], dim=0) for n in names]).contiguous()
+        if self.gated:
+            self.w_gate_up = torch.stack([torch.cat([to(tensors[n["gate"]]), to(tensors[n["up"]])], dim=0) for n in names]).contiguous()
+        else:                                    # [E, F, D]: one product an expert
+            self.w_gate_up = torch.stack([to(tensors[n["up"]]) for n in names]).contiguous()
         self.w_down = torch.stack([to(tensors[n["down"]]) for n in names]).contiguous()
         if self.shared is not None:
             self.shared.bind(tensors, dtype, device)
 
-    def forward_parts(self, normed: torch.Tensor):
+    takes_stream = True        # forward(..., stream=x32): an expert that returns its input returns the 32-bit rows
+
+    def forward_parts(self, normed: torch.Tensor, stream: Optional[torch.Tensor] = None):
         """(parts float32 [T, top, D], shared expert's output float32 [T, D] or None, its gate's logit float32 [T] or
-        None): the result is sum_k parts[:, k] + sigmoid(logit) * shared."""
+        None): the result is sum_k parts[:, k] + sigmoid(logit) * shared.  stream: the 32-bit rows that `normed` is a
+        copy of, where the layer has no norm in front of this part (identity experts then return those)."""
         T, dev = normed.shape[0], normed.device
         n_logits = self.router.shape[0]
         logits = scratch_buf("moe.logits", (T, n_logits), torch.float32, dev)
         ops.linear(normed, self.router, logits, None, self.router_bias)
-        routing = ops.moe_route(logits, self.E, self.top, ops.moe_tile_rows(normed, self.w_gate_up, self.dtype, self.top),
-                                self.weights)
+        routing = ops.moe_route(logits, self.n_out, self.top, ops.moe_tile_rows(normed, self.w_gate_up, self.dtype, self.top, self.F),
+                                self.weights, self.choice_bias, self.n_identity)
         act = scratch_buf("moe.act", (T * self.top, self.F), self.dtype, dev)
         parts = scratch_buf("moe.parts", (T, self.top, self.hidden), torch.float32, dev)
         ops.moe_experts(normed, self.w_gate_up, self.w_down, routing, self.top, act, parts, self.act, self.weight_on, self.limit,
                         self.alpha)
+        if self.n_identity:
+            ops.moe_identity(stream if stream is not None else normed, routing, self.top, self.E, parts)
         if self.shared is None:
             return parts, None, None
         shared_out = scratch_buf("moe.shared", (T, self.hidden), torch.float32, dev)
         self.shared.forward(normed, shared_out, accumulate=False)
-        return parts, shared_out, logits[:, self.E]          # the gate's logit: whoever adds the terms takes its sigmoid
+        return parts, shared_out, logits[:, self.n_out]      # the gate's logit: whoever adds the terms takes its sigmoid
 
     def add_parts(self, terms, residual: torch.Tensor, accumulate: bool = True) -> None:
         """Adds what forward_parts returned into `residual` (a token's terms in the order of its choices).  A block that
@@ -173,5 +203,6 @@ class MoEFeedForward(Part):
         parts, extra, gate = terms
         ops.rmsnorm_add(parts, None, 0.0, residual, extra, gate, gate_sigmoid=True, accumulate=accumulate)
 
-    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
-        self.add_parts(self.forward_parts(normed), residual, accumulate)
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True,
+                stream: Optional[torch.Tensor] = None) -> None:
+        self.add_parts(self.forward_parts(normed, stream), residual, accumulate)

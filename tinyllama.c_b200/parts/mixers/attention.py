@@ -11,7 +11,10 @@ Options beyond that, each a constructor argument: tensor names of one's own; a s
 its projection, so that the kernels see one head size); a rotation of neighbouring pairs (2i, 2i+1); queries and
 keys scaled to unit root mean square per head after the rotation (no weight); and an output gate, the
 concatenated heads times the sigmoid of one more projection of the mixer's input.  A rotation of neighbours and
-the norm run as one kernel on the 32-bit projection before keys and values are stored.
+the norm run as one kernel on the 32-bit projection before keys and values are stored.  Further: biases under names of
+one's own; values that ARE the keys as projected (no value projection: the key's rows serve twice in the stacked product, so
+the cached value is the key before any norm or rotation); an RMS norm with a weight over the WHOLE query projection and the
+whole key projection (all heads together) before the rotation; scores capped by tanh; a sink of score 0 in the softmax.
 """
 from __future__ import annotations
 
@@ -21,7 +24,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ... import ops
-from ..base import KVRequest, LayerCache, Part, PartSpec, StepInfo, WeightSpec, act_empty, register_mixer, scratch_buf
+from ..base import KVRequest, LayerCache, Part, PartSpec, StepInfo, WeightSpec, act_empty, register_mixer, scratch_buf, to_vec
 from ..linear import StackedLinear
 
 
@@ -31,12 +34,17 @@ class AttentionMixer(Part):
                  position: PartSpec, bias: bool = False, window: Optional[int] = None, in_scale: float = 1.0,
                  out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv",
                  names: Optional[Dict[str, str]] = None, scale: Optional[float] = None, v_dim: Optional[int] = None,
-                 qk_norm_eps: Optional[float] = None, gate: Optional[str] = None):
+                 qk_norm_eps: Optional[float] = None, gate: Optional[str] = None, values: str = "projection",
+                 whole_norm: Optional[Dict[str, object]] = None, softcap: float = 0.0, sink: bool = False):
         """names: tensor names of q, k, v, o (and g, the gate's projection) after the prefix, where they are not the
         q_proj.weight ... of the architecture's checkpoints (biases then take no part).  scale: what scores are
         multiplied by (default head_dim ** -0.5).  v_dim: size of a value head (default head_dim).  qk_norm_eps: queries
         and keys are divided by sqrt(mean(x^2) + eps) per head after the rotation.  gate: "sigmoid" or "silu" of the
-        projection named g multiplies the heads' results."""
+        projection named g multiplies the heads' results.  names may also give q_bias, k_bias, v_bias.  values "keys":
+        v = the key projection (with its bias) as it is before norm and rotation; there is no v tensor.  whole_norm =
+        dict(q=name, k=name, eps=...): q <- q / sqrt(mean(q^2) + eps) * w_q over all H * head_dim values at once, k
+        likewise, before the rotation.  softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  sink: the
+        softmax's denominator is 1 + sum exp(score)."""
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
         if not (1 <= int(head_dim) <= ops.MAX_HEAD_DIM):
@@ -65,35 +73,63 @@ class AttentionMixer(Part):
         # keys and values (which rotate split-half pairs themselves) then rotate nothing
         self.pre_transform = layout == "interleaved" or self.qk_norm_eps is not None
         if names is not None and bias:
-            raise ValueError("attention: tensor names of one's own take no biases")
+            raise ValueError("attention: tensor names of one's own name their biases themselves (q_bias, k_bias, v_bias)")
+        if values not in ("projection", "keys"):
+            raise ValueError(f"attention: values '{values}' (projection or keys)")
+        if values == "keys" and (self.v_dim != self.qk_dim or key_scale != 1.0):
+            raise ValueError("attention: values that are the keys have the keys' size and no multiplier of their own")
+        self.values, self.softcap, self.sink = values, float(softcap), bool(sink)
+        if self.softcap < 0:
+            raise ValueError(f"attention: a score cap of {softcap}")
+        self.whole_norm = dict(whole_norm) if whole_norm else None
+        if self.whole_norm and (self.qk_dim != self.hd or not {"q", "k", "eps"} <= set(self.whole_norm)):
+            raise ValueError("attention: a norm over the whole projection needs q, k (weight names) and eps, and unpadded heads")
         nm = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight")
         nm.update(names or {})
         if self.gate and "g" not in nm:
             raise ValueError("attention: an output gate needs the name of its projection ('g')")
-        b = (lambda n: prefix + n + ".bias") if bias else (lambda n: None)
+        b = (lambda n: prefix + n + ".bias") if bias else (lambda n: prefix + nm[n[0] + "_bias"] if n[0] + "_bias" in nm else None)
         qk_heads = lambda n: (n, self.qk_dim, self.hd) if self.qk_dim != self.hd else None
         v_heads = lambda n: (n, self.v_dim, self.hd) if self.v_dim != self.hd else None
         self.qkv = StackedLinear(hidden)
         self.q_off = self.qkv.add(prefix + nm["q"], self.H * self.hd, b("q_proj"), in_scale, heads=qk_heads(self.H))
         self.k_off = self.qkv.add(prefix + nm["k"], self.KV * self.hd, b("k_proj"), in_scale, key_scale, heads=qk_heads(self.KV))
-        self.v_off = self.qkv.add(prefix + nm["v"], self.KV * self.hd, b("v_proj"), in_scale, heads=v_heads(self.KV))
+        if values == "keys":          # the key's rows once more: what is cached as the value is the key as projected
+            self.v_off = self.qkv.add(prefix + nm["k"], self.KV * self.hd, b("k_proj"), in_scale)
+        else:
+            self.v_off = self.qkv.add(prefix + nm["v"], self.KV * self.hd, b("v_proj"), in_scale, heads=v_heads(self.KV))
         self.g_off = self.qkv.add(prefix + nm["g"], self.H * self.hd, None, in_scale, heads=v_heads(self.H)) if self.gate else None
         self.o = StackedLinear(self.H * self.hd, in_heads=v_heads(self.H))
         self.o.add(prefix + nm["o"], hidden, b("o_proj"), 1.0, out_scale)
         self.dtype = None
+        self.prefix = prefix
+        self.q_norm_w = self.k_norm_w = None
 
     @property
     def single_token_launches(self) -> int:
         """Kernels that mix() launches in a one-token step: one where the fused kernel serves (a
         bfloat16 cache, a head size it is built for, a position part with a rotation table), else
         rotation + split keys + merge."""
-        fused = self.dtype == torch.bfloat16 and self.position.rotation_table() is not None \
+        fused = self.dtype == torch.bfloat16 and self.position.rotation_table() is not None and not self._own_softmax \
             and ops.library().tlc_attention_decode_fused_ok(self.H, self.KV, self.hd) \
             and not ops.DISABLE_FUSED_DECODE_ATTENTION
-        return (1 if fused else 3) + int(self.pre_transform) + int(self.gate is not None)
+        return (1 if fused else 3) + int(self.pre_transform) + int(self.gate is not None) + int(self.whole_norm is not None)
+
+    @property
+    def _own_softmax(self) -> bool:
+        """A capped score or a sink: served by the warp kernels and the split-key kernels of single tokens."""
+        return self.softcap > 0 or self.sink
 
     def weight_specs(self) -> List[WeightSpec]:
-        return self.qkv.weight_specs() + self.o.weight_specs() + self.position.weight_specs()
+        specs, seen = [], set()
+        for sp in self.qkv.weight_specs() + self.o.weight_specs() + self.position.weight_specs():
+            if sp.name not in seen:               # (values that are the keys list the key's tensors twice)
+                seen.add(sp.name)
+                specs.append(sp)
+        if self.whole_norm:
+            specs += [WeightSpec(self.prefix + self.whole_norm["q"], (self.H * self.hd,), "ones"),
+                      WeightSpec(self.prefix + self.whole_norm["k"], (self.KV * self.hd,), "ones")]
+        return specs
 
     def cache_requests(self) -> list:
         return [KVRequest(self.cache_key, self.KV, self.hd, self.window)]
@@ -103,6 +139,9 @@ class AttentionMixer(Part):
         self.qkv.bind(tensors, dtype, device)
         self.o.bind(tensors, dtype, device)
         self.position.bind(tensors, dtype, device)
+        if self.whole_norm:
+            self.q_norm_w = to_vec(tensors[self.prefix + self.whole_norm["q"]], device)
+            self.k_norm_w = to_vec(tensors[self.prefix + self.whole_norm["k"]], device)
         self._no_rotation = torch.zeros(0, dtype=torch.float32, device=device)
         # arrival counters of the one-kernel attention of single-token steps: this mixer's own, so that no other
         # mixer, model or stream ever shares them; made here, outside any stream capture
@@ -136,6 +175,9 @@ class AttentionMixer(Part):
         holds at most that many SMs (a block that runs another mixer beside this one leaves it the rest)."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
+        if self.whole_norm:           # over all heads at once, before any rotation (the value columns keep the projection)
+            ops.qk_whole_norm(qkv, self.q_off, self.H * self.hd, self.q_norm_w, self.k_off, self.KV * self.hd, self.k_norm_w,
+                              float(self.whole_norm["eps"]))
         table = self.position.rotation_table()
         if table is None:
             # not a rotation: the part changes q and k in place; what is stored below is its result
@@ -145,7 +187,7 @@ class AttentionMixer(Part):
             ops.qk_rotate_norm(qkv, self.q_off, self.k_off, self.H, self.KV, self.hd, self.qk_dim, table,
                                getattr(self.position, "layout", "split_half") == "interleaved", self.qk_norm_eps, step.positions)
             table = self._no_rotation
-        if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
+        if step.max_new == 1 and not self._own_softmax and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
             att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
@@ -160,7 +202,7 @@ class AttentionMixer(Part):
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, self.scale, self.window or 0,
                       step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context,
-                      max_blocks)
+                      max_blocks, softcap=self.softcap, sink=self.sink)
         return self._gated(att, qkv)
 
     def _gated(self, att: torch.Tensor, qkv: torch.Tensor) -> torch.Tensor:

@@ -29,7 +29,11 @@ class Mamba2Mixer(Part):
     def __init__(self, hidden: int, d_ssm: int, n_heads: int, d_head: int, n_groups: int, d_state: int, d_conv: int,
                  prefix: str, eps: float, conv_bias: bool = True, proj_bias: bool = False, rms_norm: bool = True,
                  norm_before_gate: bool = False, slice_scales: Sequence[float] = (1.0,) * 5, in_scale: float = 1.0,
-                 out_scale: float = 1.0, cache_key: str = "mamba", scan_chunk: int = ops.SSD_CHUNK):
+                 out_scale: float = 1.0, cache_key: str = "mamba", scan_chunk: int = ops.SSD_CHUNK,
+                 names: Optional[Dict[str, str]] = None, norm_groups: Optional[int] = None):
+        """names: tensor names after the prefix of in_proj, out_proj, conv, conv_bias, A_log, D, dt_bias, norm where they are
+        not the in_proj.weight ... of the architecture's checkpoints (the convolution's weight is then [channels, taps]).
+        norm_groups: into how many equal parts the gated norm cuts a row (default: n_groups)."""
         if n_heads * d_head != d_ssm or n_heads % n_groups or d_ssm % n_groups:
             raise ValueError("mamba2: n_heads*d_head must equal d_ssm and both be multiples of n_groups")
         if not (1 <= int(d_state) <= ops.MAX_STATE_SIZE):
@@ -42,6 +46,13 @@ class Mamba2Mixer(Part):
             raise ValueError(f"mamba2: {n_heads} heads exceed the kernels' limit of {ops.MAX_HEADS}")
         self.hidden, self.Di, self.Hs, self.P = int(hidden), int(d_ssm), int(n_heads), int(d_head)
         self.G, self.N, self.K = int(n_groups), int(d_state), int(d_conv)
+        self.norm_groups = int(norm_groups) if norm_groups else self.G
+        if self.norm_groups < 1 or int(d_ssm) % self.norm_groups:
+            raise ValueError(f"mamba2: the gated norm cannot cut {d_ssm} values into {self.norm_groups} equal parts")
+        self.own_names = names is not None
+        self.nm = dict(in_proj="in_proj.weight", in_bias="in_proj.bias", out_proj="out_proj.weight", out_bias="out_proj.bias",
+                       conv="conv1d.weight", conv_bias="conv1d.bias", A_log="A_log", D="D", dt_bias="dt_bias", norm="norm.weight")
+        self.nm.update(names or {})
         self.Cd = self.Di + 2 * self.G * self.N                      # falcon_h1.c:124
         self.eps, self.rms_norm, self.norm_before_gate = float(eps), bool(rms_norm), bool(norm_before_gate)
         self.prefix, self.cache_key = prefix, cache_key
@@ -54,10 +65,10 @@ class Mamba2Mixer(Part):
         mz, mx, mb, mc, mdt = [float(v) for v in slice_scales]
         rows = [mz] * self.Di + [mx] * self.Di + [mb] * (self.G * self.N) + [mc] * (self.G * self.N) + [mdt] * self.Hs
         self.in_proj = StackedLinear(hidden)
-        self.in_proj.add(prefix + "in_proj.weight", self.Di + self.Cd + self.Hs,
-                         prefix + "in_proj.bias" if proj_bias else None, in_scale, rows)
+        self.in_proj.add(prefix + self.nm["in_proj"], self.Di + self.Cd + self.Hs,
+                         prefix + self.nm["in_bias"] if proj_bias else None, in_scale, rows)
         self.out_proj = StackedLinear(self.Di)
-        self.out_proj.add(prefix + "out_proj.weight", hidden, prefix + "out_proj.bias" if proj_bias else None,
+        self.out_proj.add(prefix + self.nm["out_proj"], hidden, prefix + self.nm["out_bias"] if proj_bias else None,
                           1.0, out_scale)
         self.conv_w = self.conv_b = self.A = self.D = self.dt_bias = self.norm_w = None
         self.dtype = None
@@ -66,13 +77,14 @@ class Mamba2Mixer(Part):
     def weight_specs(self) -> List[WeightSpec]:
         p = self.prefix
         specs = self.in_proj.weight_specs() + self.out_proj.weight_specs()
-        specs.append(WeightSpec(p + "conv1d.weight", (self.Cd, 1, self.K), "conv"))
+        nm = self.nm
+        specs.append(WeightSpec(p + nm["conv"], (self.Cd, self.K) if self.own_names else (self.Cd, 1, self.K), "conv"))
         if self.conv_bias:
-            specs.append(WeightSpec(p + "conv1d.bias", (self.Cd,), "normal"))
-        specs += [WeightSpec(p + "A_log", (self.Hs,), "a_log"), WeightSpec(p + "D", (self.Hs,), "d_skip"),
-                  WeightSpec(p + "dt_bias", (self.Hs,), "dt_bias")]
+            specs.append(WeightSpec(p + nm["conv_bias"], (self.Cd,), "normal"))
+        specs += [WeightSpec(p + nm["A_log"], (self.Hs,), "a_log"), WeightSpec(p + nm["D"], (self.Hs,), "d_skip"),
+                  WeightSpec(p + nm["dt_bias"], (self.Hs,), "dt_bias")]
         if self.rms_norm:
-            specs.append(WeightSpec(p + "norm.weight", (self.Di,), "ones"))
+            specs.append(WeightSpec(p + nm["norm"], (self.Di,), "ones"))
         return specs
 
     def cache_requests(self) -> list:
@@ -96,12 +108,13 @@ class Mamba2Mixer(Part):
         self.dtype = dtype
         self.in_proj.bind(tensors, dtype, device)
         self.out_proj.bind(tensors, dtype, device)
-        self.conv_w = to_vec(tensors[p + "conv1d.weight"].reshape(self.Cd, self.K), device)
-        self.conv_b = to_vec(tensors[p + "conv1d.bias"], device) if self.conv_bias else None
-        self.A = (-torch.exp(tensors[p + "A_log"].to(torch.float32))).to(device).contiguous()    # cpu_op.c:806-808
-        self.D = to_vec(tensors[p + "D"], device)
-        self.dt_bias = to_vec(tensors[p + "dt_bias"], device)
-        self.norm_w = to_vec(tensors[p + "norm.weight"], device) if self.rms_norm else None
+        nm = self.nm
+        self.conv_w = to_vec(tensors[p + nm["conv"]].reshape(self.Cd, self.K), device)
+        self.conv_b = to_vec(tensors[p + nm["conv_bias"]], device) if self.conv_bias else None
+        self.A = (-torch.exp(tensors[p + nm["A_log"]].to(torch.float32))).to(device).contiguous()    # cpu_op.c:806-808
+        self.D = to_vec(tensors[p + nm["D"]], device)
+        self.dt_bias = to_vec(tensors[p + nm["dt_bias"]], device)
+        self.norm_w = to_vec(tensors[p + nm["norm"]], device) if self.rms_norm else None
 
     # ---- one step --------------------------------------------------------------------------
     def input_projection(self) -> StackedLinear:
@@ -159,7 +172,7 @@ class Mamba2Mixer(Part):
         gated = out if out is not None else new("gated", (T, self.Di), self.dtype)
         if join is not None:
             join()
-        ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
+        ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.norm_groups, self.norm_before_gate, gated,
                           out_scale, y_part if in_two else None)
         return gated
 

@@ -70,3 +70,46 @@ class RMSNormShift(RMSNorm):
             raise ValueError("rmsnorm_shift: the kept row would advance twice in a step on another entry's cache")
         ops.rmsnorm_shift(x32, self.weight, self.mix, self.eps, cache.state[self.cache_key], step, out)
         return out
+
+
+@register_norm("none")
+class NoNorm(Part):
+    """No norm: the sublayer reads the residual stream itself.  forward() hands the stream over in the activation type
+    (bfloat16 products want bfloat16 inputs); a mixer that says `reads_stream = True` is given the 32-bit rows instead."""
+    identity = True
+
+    def __init__(self, width: int):
+        self.width = int(width)
+
+    def forward(self, x32: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is not None:
+            raise ValueError("norm 'none' copies whole steps; it serves no row selection")
+        ops.convert(x32, out)
+        return out
+
+
+@register_norm("rmsnorm_mean")
+class RMSNormMean(Part):
+    """How a layer joins several mixers that run side by side: every mixer's result is RMS-normed by itself with a weight
+    of its own, and the results are averaged: y = scale * sum_i rmsnorm(y_i) * w_i (scale 1/n unless given).  Where the
+    layer has a mixer output norm, residual += out_norm(y) in the same kernel."""
+
+    def __init__(self, width: int, eps: float, weight_names, scale: Optional[float] = None):
+        self.width, self.eps, self.weight_names = int(width), float(eps), tuple(weight_names)
+        if not (1 <= len(self.weight_names) <= 8):
+            raise ValueError(f"rmsnorm_mean: {len(self.weight_names)} summands (1..8)")
+        self.scale = float(scale) if scale is not None else 1.0 / len(self.weight_names)
+        self.weights: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(n, (self.width,), "ones") for n in self.weight_names]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.weights = torch.stack([to_vec(tensors[n], device) for n in self.weight_names]).contiguous()
+
+    def add_joined(self, parts: torch.Tensor, residual: torch.Tensor, out_norm: Optional[RMSNorm] = None) -> None:
+        """parts float32 [T, n, D]: the mixers' results side by side."""
+        if out_norm is not None and type(out_norm) is not RMSNorm:
+            raise ValueError("rmsnorm_mean: the norm after the join must be a plain RMS norm")
+        ops.rmsnorm_mean_add(parts, self.weights, self.eps, self.scale, residual,
+                             None if out_norm is None else out_norm.weight, 0.0 if out_norm is None else out_norm.eps)

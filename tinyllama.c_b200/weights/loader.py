@@ -86,6 +86,7 @@ def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", devi
         tensors = st.load_model_dir(model_dir)
     except st.SafetensorsError as e:
         raise WeightError(str(e)) from e
+    model.adopt_shapes({k: tuple(v.shape) for k, v in tensors.items()})     # sizes that only a tensor's shape gives
     check_tensors(model, tensors)
     model.bind({k: normalise(v) for k, v in tensors.items()}, rd, torch.device(device))
     return model
