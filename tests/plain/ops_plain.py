@@ -119,7 +119,7 @@ def rope_kv_store(qkv, q_off, k_off, v_off, q_out, k_pages, v_pages, inv_freq, p
 
 
 def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, H, KV, hd, scale, window=0,
-              decode_max_keys=0, cu_seqlens=None, start_pos=None, max_keys=0, max_blocks=0, key_ranges=0):
+              decode_max_keys=0, cu_seqlens=None, start_pos=None, max_keys=0, max_blocks=0, key_ranges=0, softcap=0.0, sink=False):
     T = q.shape[0]
     res = torch.zeros((T, H, hd), dtype=torch.float64)
     qf = _f(q).reshape(T, H, hd)
@@ -135,7 +135,12 @@ def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, 
         for h in range(H):
             g = h // (H // KV)
             sc = (K[:, g] @ qf[t, h]) * scale
-            pr = torch.softmax(sc, dim=0)
+            if softcap:
+                sc = softcap * torch.tanh(sc / softcap)
+            if sink:            # one more term of score 0 in the denominator, with no value
+                pr = torch.softmax(torch.cat([sc, sc.new_zeros(1)]), dim=0)[:-1]
+            else:
+                pr = torch.softmax(sc, dim=0)
             res[t, h] = pr @ V[:, g]
     out.copy_(res.reshape(T, H * hd).to(out.dtype))
 
