@@ -75,7 +75,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int n_tiles, int H,
                             int KV, float scale_log2, int window, int out_ld, int n_split, float* __restrict__ part_o,
-                            float* __restrict__ part_ml, ErrWords* err) {
+                            float* __restrict__ part_ml, float cap_in, float cap_out, int sink, ErrWords* err) {
   tlc_pdl(out);
   using L_ = FaSmem<HD>;
   constexpr int TCOLS = HD == 128 ? 512 : 256;            // the groups' scores at 0 and 64, their outputs at 128 and 128 + hd
@@ -255,6 +255,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free(wg));             // the scores are in registers: the buffer may take tile j + 2
+      if (cap_in > 0.f) {
+        // a capped score: s <- cap tanh(s scale / cap), left divided by the scale (what follows multiplies by it);
+        // tanh(x) = 1 - 2 / (e^(2x) + 1), cap_in = 2 log2(e) scale / cap, cap_out = cap / scale
+#pragma unroll
+        for (int c = 0; c < 64; c++) {
+          const float e = ex2_quick(__uint_as_float(sr[c]) * cap_in);
+          sr[c] = __float_as_uint(fmaf(-cap_out, __fdividef(2.0f, e + 1.0f), cap_out));
+        }
+      }
       const int kbase = (tile_lo + j) * BN;
       if (window > 0 || kbase + BN - 1 > p0) {
 #pragma unroll
@@ -318,11 +327,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     workers_sync();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const float m0 = xch[r], m1 = xch[BM + r];
-    const float m_all = fmaxf(m0, m1);
-    const float w0 = m0 == -INFINITY ? 0.f : ex2_quick(m0 - m_all), w1 = m1 == -INFINITY ? 0.f : ex2_quick(m1 - m_all);
-    const float l_all = xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1;
     const bool whole = n_split == 1;                      // else the sums stay unnormalised: another kernel adds the ranges
+    const bool with_sink = sink && whole;                 // one more term of score 0 in the denominator (ranges: at the merge)
+    const float m0 = xch[r], m1 = xch[BM + r];
+    const float m_all = with_sink ? fmaxf(fmaxf(m0, m1), 0.f) : fmaxf(m0, m1);
+    const float w0 = m0 == -INFINITY ? 0.f : ex2_quick(m0 - m_all), w1 = m1 == -INFINITY ? 0.f : ex2_quick(m1 - m_all);
+    const float l_all = xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1 + (with_sink ? ex2_quick(-m_all) : 0.f);
     const float inv = whole ? 1.0f / l_all : 1.0f;
     const float f0 = w0 * inv, f1 = w1 * inv;
     const bool has0 = n > 0, has1 = n > 1;                // the group had a tile at all (else its accumulator was never written)
@@ -377,7 +387,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 constexpr int TC_MAX_SPLIT = 8;
 __global__ void __launch_bounds__(128)
 attention_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                          int H, int hd, int n_split, int out_ld) {
+                          int H, int hd, int n_split, int out_ld, int sink) {
   tlc_pdl(part_o, part_ml, out);
   const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= H) return;
@@ -389,7 +399,8 @@ attention_tc_merge_kernel(const float* __restrict__ part_o, const float* __restr
     lz[z] = z < n_split ? part_ml[(at + z) * 2 + 1] : 0.f;
     if (lz[z] > 0.f) m = fmaxf(m, mz[z]);
   }
-  float w[TC_MAX_SPLIT], l = 0.f;
+  if (sink) m = fmaxf(m, 0.f);                           // the sink: a range of its own with maximum 0, sum 1 and no values
+  float w[TC_MAX_SPLIT], l = sink ? exp2f(-m) : 0.f;
 #pragma unroll
   for (int z = 0; z < TC_MAX_SPLIT; z++) {
     w[z] = lz[z] > 0.f ? exp2f(mz[z] - m) : 0.f;
@@ -436,7 +447,8 @@ template <int HD>
 int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, long long n_page_rows,
         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
         __nv_bfloat16* out, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
-        int p_max, int T, int out_ld, int max_blocks, int n_split, float* part_o, float* part_ml, cudaStream_t stream) {
+        int p_max, int T, int out_ld, int max_blocks, int n_split, float* part_o, float* part_ml, float softcap, int sink,
+        cudaStream_t stream) {
   static bool configured = false;
   const int smem = FaSmem<HD>::total(p_max);
   TLC_REQUIRE(smem <= 220 * 1024, "attention(prefill, tcgen05): %d key tiles need %d bytes of shared memory", p_max, smem);
@@ -453,11 +465,12 @@ int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat1
   const int blocks = (int)(max_blocks > 0 && max_blocks < items ? max_blocks : items);
   tlc_launch(attention_prefill_tc_kernel<HD>, dim3(blocks), dim3(THREADS), (size_t)smem, stream, mq, mk, mv,
              block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, n_tiles_bound, H, KV, scale * 1.4426950408889634f,
-             window, out_ld, n_split, part_o, part_ml, tlc_error_words());
+             window, out_ld, n_split, part_o, part_ml, softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f,
+             softcap > 0.f ? softcap / scale : 0.f, sink, tlc_error_words());
   TLC_CHECK_LAUNCH("attention(prefill, tcgen05)");
   if (n_split > 1) {
     tlc_launch(attention_tc_merge_kernel, dim3(T, (H + 3) / 4), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, H,
-               HD, n_split, out_ld);
+               HD, n_split, out_ld, sink);
     TLC_CHECK_LAUNCH("attention(prefill, tcgen05, merge)");
   }
   return 0;
@@ -489,11 +502,14 @@ extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
 // n_split > 1 (at most 8; tlc_attention_prefill_tc_splits suggests it): the keys of every row tile are cut into
 // that many ranges that run as items of their own; part_o [T, H, n_split, hd] and part_ml [T, H, n_split, 2]
 // (32-bit) hold the ranges' results until a second kernel has added them up.
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale (scale != 0 then); sink: one more term of
+// score 0 in the softmax's denominator, which carries no value.
 extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                                         const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                                         int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
-                                        int n_split, float* part_o, float* part_ml, cudaStream_t stream) {
+                                        int n_split, float* part_o, float* part_ml, float softcap, int sink,
+                                        cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0 || T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;
   TLC_REQUIRE(tlc_attention_prefill_tc_ok(TLC_BF16, hd, H, KV), "attention(prefill, tcgen05): %d heads, %d key/value heads of size %d are not built", H, KV, hd);
@@ -509,7 +525,7 @@ extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, cons
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   if (hd == 64)
     return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, stream);
+                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, softcap, sink, stream);
   return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, stream);
+                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, softcap, sink, stream);
 }

@@ -78,7 +78,7 @@ _SIGNATURES = {
                                    _vp, _i, _i, _vp]),
     "tlc_attention_prefill_tc_ok": (_i, [_i, _i, _i, _i]),
     "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
-                                      _i, _i, _i, _i, _vp, _vp, _vp]),
+                                      _i, _i, _i, _i, _vp, _vp, _f, _i, _vp]),
     "tlc_attention_prefill_tc_splits": (_i, [_i, _i, _i]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
                             _i, _i, _i, _i, _i, _i, _vp]),
@@ -586,7 +586,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     other kernels beside it; the result does not depend on it.  key_ranges > 0 fixes into how many ranges that
     kernel cuts the keys of a row tile (0: chosen: more than one for few rows over many keys).  softcap > 0: scores are
     softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one more term of score 0, which
-    carries no value (both served by the warp kernels and the split-key kernels of single tokens)."""
+    carries no value (both served by the tcgen05 kernel of prompts, the warp kernels and the split-key kernels of single
+    tokens)."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.dtype != q.dtype or k_pages.dtype != q.dtype:
@@ -601,7 +602,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
               int(window or 0), int(decode_max_keys), out_ld, float(softcap), int(bool(sink)), _stream())
         return
-    tiled = not (softcap > 0 or sink) and decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
+    own_softmax = softcap > 0 or sink
+    tiled = decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
         and hd in (64, 128) and not DISABLE_TILED_ATTENTION
     if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
             and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
@@ -615,9 +617,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_prefill_tc", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
               block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(),
               out.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
-              out_ld, int(max_blocks), int(n_split), _p(part_o), _p(part_ml), _stream())
+              out_ld, int(max_blocks), int(n_split), _p(part_o), _p(part_ml), float(softcap), int(bool(sink)), _stream())
         return
-    if tiled:
+    if tiled and not own_softmax:
         B = slots.numel()
         n_tiles = T // 64 + B
         chunk = ctypes.c_int(0)

@@ -117,7 +117,7 @@ class AttentionMixer(Part):
 
     @property
     def _own_softmax(self) -> bool:
-        """A capped score or a sink: served by the warp kernels and the split-key kernels of single tokens."""
+        """A capped score or a sink: served by the tcgen05 kernel of prompts, the warp kernels and the split-key kernels of single tokens."""
         return self.softcap > 0 or self.sink
 
     def weight_specs(self) -> List[WeightSpec]:
