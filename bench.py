@@ -245,9 +245,9 @@ def main() -> int:
     ap.add_argument("--no-big", dest="big", action="store_false", help="skip the 3B and 7B workloads among the points")
     ap.add_argument("--no-pairs", action="store_true", help="run the linear layers on single blocks (128 x 256 tiles) instead "
                     "of pairs of blocks on 256 x 256 tiles: the comparison behind profiles/linear_tcgen05_prefill_2048.md")
-    ap.add_argument("--design", default=None, choices=["turevik", "porarax"], help="instead of the benchmark line: prefill and decode "
+    ap.add_argument("--design", default=None, choices=["turevik", "porarax", "sogazen"], help="instead of the benchmark line: prefill and decode "
                     "throughput of this design at layer sizes of a real model's order (random weights), beside the library's "
-                    "closest other design (Falcon-H1 for turevik, Turevik for porarax) at equal width and layer count")
+                    "closest other design (Falcon-H1 for turevik and sogazen, Turevik for porarax) at equal width and layer count")
     ap.add_argument("--sizes-only", default=None, choices=["width 2048", "width 3072"], help="with --design: one of the two sizes")
     ap.add_argument("--ref-budget", type=float, default=600.0, help="seconds the reference arm may take (it runs fewer "
                     "layers, and says so, where all of them would take longer)")
@@ -427,9 +427,55 @@ def porarax_work(cfg, batch, context, T):
     return fixed * 2 + expert_bytes + cache_bytes, 2.0 * (fixed - V * D + expert_params) * T + 2.0 * V * D + mix_flops
 
 
+def sogazen_config(width, heads, kv_heads, ssm_heads, ssm_vdim, state, wkv_heads, ff, experts, identity, top, expert_ff, vocab):
+    """Four layers with every kind of sublayer: attention beside Mamba2 with a dense feed-forward; the same with experts;
+    the wkv mixer with experts; attention beside Mamba2 with experts.  The attention and Mamba2 sizes are Falcon-H1's at
+    that width."""
+    par = dict(type="parallel", mixer=dict(
+        left=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0, rot=dict(base=1e6, dims=64)),
+        right=dict(heads=ssm_heads, vdim=ssm_vdim, state=state, groups=1, norm_groups=2, conv=4)))
+    moe = dict(kind="moe", router=dict(experts=experts, identity=identity, top=top), expert=dict(ff=expert_ff))
+    return dict(architecture="Sogazen", vocab=vocab, width=width, norm=dict(eps=1e-6), logit_softcap=30.0, layers=[
+        dict(par, mlp=dict(kind="dense", ff=ff, limit=7.0)), dict(par, mlp=moe),
+        dict(type="wkv", mixer=dict(heads=wkv_heads, dim=64), mlp=moe), dict(par, mlp=moe)])
+
+
+def sogazen_work(cfg, batch, context, T):
+    """(bytes a decode step of `batch` sequences at `context` must read, FLOPs of a prompt of T tokens)."""
+    D, V = cfg["width"], cfg["vocab"]
+    fixed, cache_bytes, mix_flops, expert_bytes, expert_params = V * D, 0, 0.0, 0.0, 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "parallel":
+            a, s = m["left"], m["right"]
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            fixed += (H * dk + G * dk) * D + D * H * dv                  # q, k (also the values), o
+            cache_bytes += batch * context * G * (dk + dv) * 2
+            mix_flops += 2.0 * H * (dk + dv) * T * (T + 1) / 2
+            inner, N = s["heads"] * s["vdim"], s["state"]
+            fixed += (2 * inner + 2 * s["groups"] * N + s["heads"]) * D + D * inner
+            cache_bytes += batch * (s["heads"] * s["vdim"] * N + (s["conv"] - 1) * (inner + 2 * s["groups"] * N)) * 4
+            mix_flops += 6.0 * s["heads"] * s["vdim"] * N * T             # the state's update and read-out
+        else:
+            HD, R = m["heads"] * m["dim"], max(8, D // 16)
+            fixed += 4 * HD * D + R * D + HD * R + D * HD
+            cache_bytes += batch * (m["heads"] * m["dim"] * m["dim"] + D) * 4
+            mix_flops += 4.0 * m["heads"] * m["dim"] * m["dim"] * T       # the read-out S^T r and the update of S
+        mlp = layer["mlp"]
+        if mlp["kind"] == "dense":
+            fixed += 3 * D * mlp["ff"]
+            continue
+        E, I, top, F = mlp["router"]["experts"], mlp["router"]["identity"], mlp["router"]["top"], mlp["expert"]["ff"]
+        fixed += (E + I) * D
+        expert_params += top * (E / (E + I)) * 2 * D * F                  # a choice is an expert with weights E times in E + I
+        touched = E * (1.0 - (1.0 - 1.0 / (E + I)) ** (batch * top))      # expected distinct experts of a step
+        expert_bytes += touched * 2 * D * F * 2
+    return fixed * 2 + expert_bytes + cache_bytes, 2.0 * (fixed - V * D + expert_params) * T + 2.0 * V * D + mix_flops
+
+
 def design_compare(args) -> int:
-    """Another design beside the library's closest one at equal width and layer count (Turevik beside Falcon-H1, Porarax
-    beside Turevik): a prompt of --prefill-tokens tokens and decode steps at batch 8 and 64 from --prompt-len-token
+    """Another design beside the library's closest one at equal width and layer count (Turevik and Sogazen beside Falcon-H1,
+    Porarax beside Turevik): a prompt of --prefill-tokens tokens and decode steps at batch 8 and 64 from --prompt-len-token
     prompts, each as time and as a fraction of the measured peak for the bytes a step must read (decode) or the FLOPs a
     prompt needs (prefill)."""
     import torch
@@ -442,11 +488,15 @@ def design_compare(args) -> int:
         cases = {"width 2048": (porarax_config(2048, 16, 4, 256, 768, 1024, 32, 4, 1024, 65536), turevik["width 2048"]),
                  "width 3072": (porarax_config(3072, 24, 8, 256, 1024, 1024, 64, 6, 2048, 130048), turevik["width 3072"])}
         beside = "turevik"
+    elif args.design == "sogazen":
+        cases = {"width 2048": (sogazen_config(2048, 8, 2, 48, 64, 256, 32, 4096, 32, 4, 4, 1024, 65536), dict(CONFIG_1P5B, num_hidden_layers=4)),
+                 "width 3072": (sogazen_config(3072, 12, 2, 24, 128, 256, 48, 12288, 64, 8, 6, 2048, 130048), dict(CONFIG_7B, num_hidden_layers=4))}
+        beside = "falcon_h1"
     else:
         cases = {"width 2048": (turevik["width 2048"], dict(CONFIG_1P5B, num_hidden_layers=4)),
                  "width 3072": (turevik["width 3072"], dict(CONFIG_7B, num_hidden_layers=4))}
         beside = "falcon_h1"
-    work = {"turevik": turevik_work, "porarax": porarax_work}
+    work = {"turevik": turevik_work, "porarax": porarax_work, "sogazen": sogazen_work}
     if args.sizes_only:
         cases = {k: v for k, v in cases.items() if k == args.sizes_only}
     for name, (tcfg, fcfg) in cases.items():

@@ -88,3 +88,249 @@ def test_capped_scores_and_sink_of_any_rows_and_of_single_tokens(dtype, H, KV, h
     for max_keys in (701, 1024):
         cmp("attention", [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(5, H * hd, dtype=DT[dtype]), H, KV,
                           hd, 1.0 / math.sqrt(hd), 0, max_keys, None, None, 0, 0, 0, softcap, sink], [7], tol_of=KTOL[DT[dtype]] * 2)
+
+
+# ---- the attention mixer whose values are its keys ---------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("H,G,d,rot,cap", [(4, 2, 16, 6, 3.0), (9, 1, 64, 64, 20.0), (3, 3, 24, 0, 40.0), (8, 2, 128, 32, 12.0)])
+def test_attention_mixer_with_keys_as_values(dtype, H, G, d, rot, cap):
+    """Biases on q and k, one norm over all query heads and one over all key heads, part of every head rotated, the cap,
+    the sink; what is cached as a value is the key as projected.  Prompts in one step, then single tokens."""
+    g = np.random.default_rng(11)
+    D = 40
+    m = dict(heads=H, kv_heads=G, dim=d, vdim=d, scale=float(d ** -0.5) * 1.7, softcap=cap, rot=dict(base=1000.0, dims=rot))
+    W = {"a.q": draw(g, (H * d, D), 0.3, dtype), "a.k": draw(g, (G * d, D), 0.3, dtype), "a.o": draw(g, (D, H * d), 0.2, dtype),
+         "a.q.b": draw(g, (H * d,), 0.5, dtype), "a.k.b": draw(g, (G * d,), 0.5, dtype),
+         "a.q.norm": 1.0 + draw(g, (H * d,), 0.3, dtype), "a.k.norm": 1.0 + draw(g, (G * d,), 0.3, dtype)}
+    position = PartSpec("position", "rope_neox", dict(head_dim=d, theta=1000.0, rope_dim=rot)) if rot else \
+        PartSpec("position", "none", dict(head_dim=d))
+    part = PartSpec("mixer", "attention", dict(
+        hidden=D, n_heads=H, n_kv_heads=G, head_dim=d, v_dim=d, prefix="a.", position=position,
+        names=dict(q="q", k="k", o="o", q_bias="q.b", k_bias="k.b"), values="keys", scale=m["scale"],
+        whole_norm=dict(q="q.norm", k="k.norm", eps=1e-5), softcap=cap, sink=True)).build()
+    part.bind({k: torch.tensor(v, dtype=DT[dtype] if v.ndim == 2 else torch.float32) for k, v in W.items()}, DT[dtype], "cuda")
+    rows = [draw(g, (n + DECODED, D), 1.0, dtype) for n in LENS]
+
+    def forward(x, step, views):
+        out = torch.zeros((x.shape[0], D), dtype=torch.float32, device="cuda")
+        part.forward(x, step, views[0], out)
+        return out
+    got = run_steps(forward, part.cache_requests(), rows, dtype, DT[dtype])
+    want = [plain.key_value_attention(x, W, "a.", m, 1e-5, np.arange(len(x)), rnd_of(dtype)) for x in rows]
+    compare(got, want, dtype, "attention with keys as values", tol=3e-5 if dtype == "float32" else 4e-2)
+
+
+# ---- the mixer with a decaying matrix state ------------------------------------------------------------------------------
+class _Step:
+    pass
+
+
+def _wkv_plain(r, k, v, w, u):
+    T, H, d = r.shape
+    o, S = np.zeros((T, H, d)), np.zeros((H, d, d))
+    for t in range(T):
+        for h in range(H):
+            kv = np.outer(k[t, h], v[t, h])
+            o[t, h] = (S[h] + u[h][:, None] * kv).T @ r[t, h]
+            S[h] = w[t, h][:, None] * S[h] + kv
+    return o
+
+
+@pytest.mark.parametrize("H,d", [(2, 8), (3, 32), (2, 64), (1, 72), (2, 40), (1, 130)])
+def test_wkv_state_keeps_what_was_written_hundreds_of_tokens_back(H, d):
+    """Two sequences in one step, then continued in portions and single tokens.  The decay stays within 1e-3 of one and
+    token 3 writes a large value along a key that later receptances repeat, so hundreds of tokens on the read-out is
+    still mostly that value: a state that is lost, reset, decayed twice or mixed up between sequences, heads or slots
+    shows.  The bonus differs by far from 1, so leaving it out, or giving it to the state, shows at once.  The slots held
+    rubbish before, and slot 0 is then used again by a third sequence."""
+    lens, portions = [330, 97], [[203, 1, 1, 61, 64], [90, 1, 1, 3, 2]]
+    state = torch.full((3, H, d, d), 3.0, device="cuda")
+    u = np.random.default_rng(3).standard_normal((H, d)) * 2.0 + 3.0
+
+    def make(T, seed):
+        g = np.random.default_rng(seed)
+        r, k = g.standard_normal((T, H, d)), g.standard_normal((T, H, d)) * 0.3
+        unit = k[3] / np.sqrt((k[3] * k[3]).sum(-1, keepdims=True))
+        for t in range(T):                                            # no other token writes along token 3's key
+            if t != 3:
+                k[t] -= (k[t] * unit).sum(-1, keepdims=True) * unit
+        k[3] = unit
+        r[5:] = 0.05 * r[5:] + unit[None] * 2.0                       # later tokens ask for token 3's key
+        v = g.standard_normal((T, H, d)) * 0.1
+        v[3] = g.standard_normal((H, d)) * 3.0
+        a = np.log(-np.log(1.0 - 1e-3 * g.random((T, H, d))))        # w = exp(-exp(a)) within 1e-3 of one
+        f = lambda x: x.astype(np.float32).astype(np.float64)
+        return [f(x) for x in (r, k, v, a)]
+
+    def run(seqs, slots, cuts):
+        outs, at = [[] for _ in seqs], [0] * len(seqs)
+        HD = H * d
+        for s in range(max(len(c) for c in cuts)):
+            live = [i for i in range(len(seqs)) if s < len(cuts[i])]
+            counts = [cuts[i][s] for i in live]
+            T = sum(counts)
+            rkv = np.zeros((T, 3 * HD + 5), dtype=np.float32)       # v, r, k from columns 2, 2 + HD + 1, ...: any offsets
+            a = np.zeros((T, HD), dtype=np.float32)
+            o = 0
+            for i, n in zip(live, counts):
+                r_, k_, v_, a_ = [x[at[i]:at[i] + n].reshape(n, HD) for x in seqs[i]]
+                rkv[o:o + n, 2:2 + HD], rkv[o:o + n, 3 + HD:3 + 2 * HD], rkv[o:o + n, 5 + 2 * HD:5 + 3 * HD] = v_, r_, k_
+                a[o:o + n] = a_
+                o += n
+            step = _Step()
+            step.n_seqs, step.n_rows = len(live), T
+            step.cu_seqlens = dev(np.concatenate([[0], np.cumsum(counts)]), torch.int32)
+            step.slots = dev([slots[i] for i in live], torch.int32)
+            step.start_pos = dev([at[i] for i in live], torch.int32)
+            y = torch.empty((T, HD), device="cuda")
+            ops.wkv_scan(dev(rkv), 3 + HD, 5 + 2 * HD, 2, dev(a), dev(u), state, step, H, d, y)
+            torch.cuda.synchronize()
+            ops.check_errors()
+            y = y.cpu().numpy().astype(np.float64)
+            o = 0
+            for i, n in zip(live, counts):
+                outs[i].append(y[o:o + n])
+                at[i] += n
+                o += n
+        return [np.concatenate(x).reshape(-1, H, d) for x in outs]
+
+    want_of = lambda seq: _wkv_plain(seq[0], seq[1], seq[2], np.exp(-np.exp(seq[3])), u)
+    seqs = [make(n, 20 + i) for i, n in enumerate(lens)]
+    got = run(seqs, [2, 0], portions)
+    for i, seq in enumerate(seqs):
+        want = want_of(seq)
+        err = np.abs(got[i] - want).max()
+        assert err <= 3e-5 * np.abs(want).max(), f"sequence {i}: error {err:.3e} of {np.abs(want).max():.3e}"
+        assert np.abs(want[-1] / 2.0 - seq[2][3]).max() < 0.5 * np.abs(seq[2][3]).max()      # far on, still token 3's value
+        # the bonus shows: token 3's own read-out is u times what the state alone would give
+        assert np.abs(want[3] - _wkv_plain(seq[0][:4], seq[1][:4], seq[2][:4], np.exp(-np.exp(seq[3][:4])), np.ones((H, d)))[3]).max() > 0.1
+    third = make(40, 33)
+    got3, want3 = run([third], [0], [[1, 1, 30, 8]])[0], want_of(third)
+    assert np.abs(got3 - want3).max() <= 3e-5 * np.abs(want3).max(), "a slot used again"
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("H,d,R", [(3, 8, 5), (2, 64, 16), (1, 72, 7), (5, 16, 8)])
+def test_wkv_mixer_with_its_mixes_gate_and_norm(dtype, H, d, R):
+    """The whole mixer: five mixes with the previous token's input (kept across steps, zeros at position 0), the decay's
+    two small products, the scan, each head divided by its root mean square, the weight, the gate, the output."""
+    g = np.random.default_rng(13)
+    D, HD = 44, H * d
+    names = {k: "w." + k for k in ("r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o")}
+    names.update({"mu_" + s: "w.mu." + s for s in ("r", "k", "v", "g", "w")})
+    W = {"w." + s: draw(g, (HD, D), 0.25, dtype) for s in ("r", "k", "v", "g")}
+    W.update({"w.mu." + s: plain.bf16_round(g.random(D)) for s in ("r", "k", "v", "g", "w")})
+    W.update({"w.w1": draw(g, (R, D), 0.3, dtype), "w.w2": draw(g, (HD, R), 0.5, dtype), "w.w0": draw(g, (HD,), 1.0, dtype) - 2.0,
+              "w.u": draw(g, (H, d), 1.0, dtype), "w.norm": 1.0 + draw(g, (HD,), 0.2, dtype), "w.o": draw(g, (D, HD), 0.2, dtype)})
+    part = PartSpec("mixer", "wkv", dict(hidden=D, n_heads=H, head_dim=d, eps=1e-5, names=names, decay_rank=R)).build()
+    part.bind({k: torch.tensor(v, dtype=DT[dtype] if v.ndim == 2 and "u" != k[-1] else torch.float32) for k, v in W.items()},
+              DT[dtype], "cuda")
+    rows = [g.standard_normal((n + DECODED, D)).astype(np.float32).astype(np.float64) for n in LENS]
+
+    def forward(x, step, views):
+        out = torch.zeros((x.shape[0], D), dtype=torch.float32, device="cuda")
+        part.forward(x, step, views[0], out, accumulate=False)
+        return out
+    got = run_steps(forward, part.cache_requests(), rows, dtype, torch.float32)
+    want = [plain.wkv_mixer(x, W, "w.", dict(heads=H, dim=d), 1e-5, rnd_of(dtype)) for x in rows]
+    compare(got, want, dtype, "wkv mixer", tol=3e-5 if dtype == "float32" else 4e-2)
+
+
+# ---- the norm that joins two mixers, the dense feed-forward ----------------------------------------------------------------
+@pytest.mark.parametrize("n,D", [(2, 44), (2, 256), (3, 64)])
+def test_mixers_joined_by_their_own_norms(n, D):
+    """Every summand divided by its OWN root mean square (summands of very different sizes: a shared root mean square
+    would let the largest one drown the others), then the layer's norm on the mean."""
+    g = np.random.default_rng(14)
+    T = 37
+    parts = g.standard_normal((T, n, D)) * np.array([0.01, 30.0, 1.0][:n])[None, :, None]
+    w, outer, res = 1.0 + g.standard_normal((n, D)) * 0.2, 1.0 + g.standard_normal(D) * 0.2, g.standard_normal((T, D))
+    f32 = lambda a: np.asarray(a, dtype=np.float32).astype(np.float64)
+    parts, w, outer, res = f32(parts), f32(w), f32(outer), f32(res)
+    part = PartSpec("norm", "rmsnorm_mean", dict(width=D, eps=1e-6, weight_names=tuple(f"j{i}" for i in range(n)))).build()
+    part.bind({f"j{i}": torch.tensor(w[i], dtype=torch.float32) for i in range(n)}, torch.float32, "cuda")
+    out_norm = PartSpec("norm", "rmsnorm", dict(width=D, eps=1e-6, weight_name="o")).build()
+    out_norm.bind({"o": torch.tensor(outer, dtype=torch.float32)}, torch.float32, "cuda")
+    y = sum(plain.rms_norm(parts[:, i], w[i], 1e-6) for i in range(n)) / n
+    r = dev(res)
+    part.add_joined(dev(parts), r, out_norm)
+    want = res + plain.rms_norm(y, outer, 1e-6)
+    assert np.abs(r.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    r = dev(res)
+    part.add_joined(dev(parts), r)
+    assert np.abs(r.cpu().numpy() - (res + y)).max() <= 1e-5 * np.abs(res + y).max()
+
+
+@pytest.mark.parametrize("dtype,D,F", [("bfloat16", 256, 512), ("bfloat16", 64, 40), ("bfloat16", 44, 28), ("float32", 64, 40)])
+def test_dense_feed_forward_with_both_clamps_at_work(dtype, D, F):
+    g = np.random.default_rng(15)
+    limit = 0.9
+    W = {"f.gate": draw(g, (F, D), 0.2, dtype), "f.up": draw(g, (F, D), 0.2, dtype), "f.down": draw(g, (D, F), 0.1, dtype)}
+    part = PartSpec("feed_forward", "swiglu", dict(hidden=D, intermediate=F, prefix="f.", act="swish_clamped", limit=limit,
+                                                   alpha=plain.SWISH_ALPHA, names=dict(gate="gate", up="up", down="down"))).build()
+    part.bind({k: torch.tensor(v, dtype=DT[dtype]) for k, v in W.items()}, DT[dtype], "cuda")
+    for T in (1, 20, 100, 300):
+        x = draw(g, (T, D), 1.0, dtype)
+        out = torch.zeros((T, D), dtype=torch.float32, device="cuda")
+        part.forward(dev(x, DT[dtype]), out, accumulate=False)
+        want = plain.dense_ff(x, W, "f.", dict(limit=limit), rnd_of(dtype))
+        err = np.abs(out.cpu().numpy() - want).max()
+        assert err <= (3e-5 if dtype == "float32" else 2e-2) * np.abs(want).max(), f"T={T}: {err:.3e} of {np.abs(want).max():.3e}"
+        gate, up = x @ W["f.gate"].T, x @ W["f.up"].T
+        if T >= 100:
+            assert (gate > limit).mean() > 0.1 and (up > limit).mean() > 0.1 and (up < -limit).mean() > 0.1
+
+
+# ---- routing over all outputs with a correction, identity outputs, experts without a gate -----------------------------------
+def test_routing_where_the_correction_changes_the_choice_but_not_the_weight():
+    g = np.random.default_rng(16)
+    for E, ident, top in ((4, 4, 2), (3, 0, 3), (1, 2, 1), (6, 1, 7), (40, 5, 6)):
+        T, n = 60, E + ident
+        z = g.standard_normal((T, n + 1)).astype(np.float32)            # (one more column than outputs: it takes no part)
+        corr = (g.standard_normal(n) * 0.5).astype(np.float32)
+        corr[n - 1] = 0.9                                               # the last output is chosen far more often than its score earns
+        ids, wts, order, offsets, tile_off, _ = ops.moe_route(dev(z), n, top, 32, "softmax_all", dev(corr), ident)
+        torch.cuda.synchronize()
+        ids, wts = ids.cpu().numpy().reshape(T, top), wts.cpu().numpy().reshape(T, top)
+        W = {"m.router": np.eye(n), "m.correction": corr.astype(np.float64)}
+        mlp = dict(router=dict(experts=E, identity=ident, top=top))
+        want_ids, want_w = plain.route(z[:, :n].astype(np.float64), W, "m.", mlp)
+        changed = 0
+        for t in range(T):
+            assert list(ids[t]) == list(want_ids[t]), f"E={E}+{ident} top={top} token {t}"
+            assert np.abs(wts[t] - want_w[t]).max() <= 1e-6
+            changed += set(want_ids[t]) != set(np.argsort(-z[t, :n], kind="stable")[:top])
+        assert top == n or changed > 0
+        if top < n:
+            assert wts.sum(-1).max() < 1.0 - 1e-3                       # the weights are the scores: not renormalised
+        order, offsets = order.cpu().numpy(), offsets.cpu().numpy()
+        flat = ids.reshape(-1)
+        for e in range(E):                                              # the lists of the experts that have weights
+            assert all(flat[i] == e for i in order[offsets[e]:offsets[e + 1]])
+            assert offsets[e + 1] - offsets[e] == (flat == e).sum()
+
+
+@pytest.mark.parametrize("dtype,D,F", [("float32", 44, 20), ("bfloat16", 64, 24), ("bfloat16", 44, 12), ("bfloat16", 128, 72)])
+@pytest.mark.parametrize("E,ident,top", [(4, 4, 2), (1, 0, 1), (2, 3, 5), (6, 1, 3)])
+def test_experts_without_gates_beside_identity_outputs(dtype, D, F, E, ident, top):
+    """The part as a layer runs it: the input in the activation type for the products, the 32-bit rows for the outputs
+    that return their input."""
+    g = np.random.default_rng(17)
+    n = E + ident
+    W = {"m.router": draw(g, (n, D), 0.3, dtype), "m.correction": draw(g, (n,), 0.3, dtype)}
+    for e in range(E):
+        W[f"m.e{e}.up"], W[f"m.e{e}.down"] = draw(g, (F, D), 0.3, dtype), draw(g, (D, F), 0.3, dtype)
+    part = PartSpec("feed_forward", "moe", dict(
+        hidden=D, n_experts=E, top=top, expert_ff=F, router_name="m.router", choice_bias_name="m.correction", n_identity=ident,
+        expert_names={k: "m.e{e}." + k for k in ("up", "down")}, weights="softmax_all", weight_on="output", act="relu_squared")).build()
+    part.bind({k: torch.tensor(v, dtype=DT[dtype] if v.ndim == 2 else torch.float32) for k, v in W.items()}, DT[dtype], "cuda")
+    mlp = dict(router=dict(experts=E, identity=ident, top=top))
+    for T in (1, 33, 150):
+        x = g.standard_normal((T, D)).astype(np.float32).astype(np.float64)
+        out = torch.zeros((T, D), dtype=torch.float32, device="cuda")
+        part.forward(dev(x).to(DT[dtype]), out, accumulate=False, stream=dev(x))
+        torch.cuda.synchronize()
+        ops.check_errors()
+        want = plain.expert_ff(x, W, "m.", mlp, rnd_of(dtype))
+        err = np.abs(out.cpu().numpy() - want).max()
+        assert err <= (3e-5 if dtype == "float32" else 2e-2) * np.abs(want).max(), f"T={T}: {err:.3e} of {np.abs(want).max():.3e}"
