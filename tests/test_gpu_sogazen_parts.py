@@ -90,6 +90,53 @@ def test_capped_scores_and_sink_of_any_rows_and_of_single_tokens(dtype, H, KV, h
                           hd, 1.0 / math.sqrt(hd), 0, max_keys, None, None, 0, 0, 0, softcap, sink], [7], tol_of=KTOL[DT[dtype]] * 2)
 
 
+
+@pytest.mark.parametrize("H,KV,hd,rope,softcap,sink", [(8, 2, 128, 64, 30.0, True), (6, 1, 64, 64, 3.0, True), (6, 3, 64, 32, 0.0, True),
+                                                       (4, 4, 128, 0, 8.0, False), (2, 2, 256, 128, 5.0, True)])
+def test_capped_scores_and_sink_of_single_tokens_in_one_kernel(H, KV, hd, rope, softcap, sink):
+    """Rotation, store of the new row and attention in one launch, with the cap and the sink: a far key whose raw score
+    lies above the cap, a first row (its own key and the sink), a row whose query points away from all its keys (the
+    sink takes most); the keys in one piece a block, in several pieces that another block merges, and pieces of two rounds."""
+    g = gen(93)
+    starts = [0, 200, 63, 3300, 127, 128]
+    B = len(starts)
+    pos, row_seq, cu, _ = _step_arrays(starts, [1] * B)
+    slots, table, k_pages, v_pages = _paged_setup(g, B, [s + 1 for s in starts], KV, hd, torch.bfloat16, n_slots=7)
+    _mark_keys(k_pages, table, slots, 3, {3: 9.0, 2500: 6.0})
+    for p in range(200):
+        k_pages[int(table[int(slots[1]), p // 64]), :, p % 64, :] += 1.5
+    width = (H + 2 * KV) * hd
+    qkv = rnd(g, B, width)
+    qkv[1, :H * hd] = 0.1 * qkv[1, :H * hd] - 0.4
+    inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64),
+                           torch.arange(rope // 2, dtype=torch.float64) * 2 / max(rope, 1))).float()
+    scale = 1.3 / math.sqrt(hd)
+    k_ref, v_ref = k_pages.clone(), v_pages.clone()
+    q_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
+    ops_plain.rope_kv_store(qkv, 0, H * hd, (H + KV) * hd, q_ref, k_ref, v_ref, inv, pos, row_seq, slots, table, H, KV, hd, True)
+    out_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
+    ops_plain.attention(q_ref, k_ref, v_ref, table, pos, row_seq, slots, out_ref, H, KV, hd, scale, 0, 0, None, None, 0, 0, 0,
+                        softcap, sink)
+    counters = ops.new_arrival_counters("cuda")
+    try:
+        for max_keys, passes in ((3301, 0), (4096, 2), (3301, 1000)):
+            ops.attention_decode_fused_passes(passes)
+            k_gpu, v_gpu = k_pages.cuda(), v_pages.cuda()
+            out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
+            ops.attention_decode_fused(qkv.cuda(), 0, H * hd, (H + KV) * hd, k_gpu, v_gpu, inv.cuda(), True, table.cuda(), pos.cuda(),
+                                       row_seq.cuda(), slots.cuda(), out, H, KV, hd, scale, 0, max_keys, counters, softcap, sink)
+            torch.cuda.synchronize()
+            ops.check_errors()
+            ref = out_ref.double()
+            err = (ref - out.cpu().double()).abs().max()
+            assert err <= KTOL[torch.bfloat16] * 2.5 * ref.abs().max(), f"max_keys {max_keys}, passes {passes}: {err}"
+    finally:
+        ops.attention_decode_fused_passes(0)
+    if sink:                                        # the sink shows: without it the first row would be its own value
+        own = v_ref[int(table[int(slots[0]), 0]), :, 0, :].double().repeat_interleave(H // KV, 0).reshape(-1)
+        assert (out_ref[0].double() - own).abs().max() > 0.05 * own.abs().max()
+
+
 # ---- the attention mixer whose values are its keys ---------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("H,G,d,rot,cap", [(4, 2, 16, 6, 3.0), (9, 1, 64, 64, 20.0), (3, 3, 24, 0, 40.0), (8, 2, 128, 32, 12.0)])

@@ -85,7 +85,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
                             const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
                             float* __restrict__ part_ml, unsigned* __restrict__ arrivals,
                             __nv_bfloat16* __restrict__ out, int H, int KV, float scale, int window, int n_splits,
-                            int passes, int out_ld) {
+                            int passes, int out_ld, float softcap, int sink) {
   // Keys and values of earlier positions were stored by earlier steps and are fetched before the
   // wait on the previous kernel; the row's own projection is read after it.
   asm volatile("griddepcontrol.launch_dependents;");
@@ -255,13 +255,16 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       }
       // softmax of head `hrow` over this lane's keys, with the running maximum
       float mx = -INFINITY;
+      const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
 #pragma unroll
       for (int n = 0; n < NT_S; n++) {
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           const int key = k0 + n * 8 + cpair + e;
           const bool valid = key >= start && key < n_keys;
-          S[n][e] = valid ? S[n][e] * scale : -INFINITY;
+          float sc = S[n][e] * scale;
+          if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);        // a capped score
+          S[n][e] = valid ? sc : -INFINITY;
           mx = fmaxf(mx, S[n][e]);
         }
       }
@@ -316,7 +319,9 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       float M = -INFINITY;
 #pragma unroll
       for (int x = 0; x < FM_NW; x++) M = fmaxf(M, m_s[x * 8 + hg]);
-      float o = 0.f, l = 0.f;
+      const bool with_sink = sink && n_splits == 1;       // one more term of score 0 in the sum (splits: at their merge)
+      if (with_sink) M = fmaxf(M, 0.f);
+      float o = 0.f, l = with_sink ? expf(-M) : 0.f;
 #pragma unroll
       for (int x = 0; x < FM_NW; x++) {
         const float mw = m_s[x * 8 + hg];
@@ -346,7 +351,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  attention_merge_splits<HD, FM_NT>(part_o, part_ml, out, reinterpret_cast<float*>(smraw), smem_floats, t, g, G, H, n_splits, out_ld);
+  attention_merge_splits<HD, FM_NT>(part_o, part_ml, out, reinterpret_cast<float*>(smraw), smem_floats, t, g, G, H, n_splits, out_ld, sink);
 }
 
 int g_fused_passes = 0;       // > 0: rounds a block takes, for tests (0: chosen from the grid)
@@ -376,13 +381,14 @@ extern "C" int tlc_attention_decode_fused_ok(int H, int KV, int hd) {
 
 // qkv: float32 rows of `ld` elements with the queries, keys and values of the row at q_off, k_off,
 // v_off.  scratch: part_o [T, H, n_splits, hd], part_ml [T, H, n_splits, 2] floats with
-// n_splits <= ceil(max_keys / 128); arrivals: T * KV counters, zero before the first call.
+// n_splits <= ceil(max_keys / 128); arrivals: T * KV counters, zero before the first call.  softcap > 0: score <-
+// softcap * tanh(score / softcap) after the scale; sink: one more term of score 0 in the softmax's denominator.
 extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, int k_off, int v_off, void* k_pages,
                                         void* v_pages, const float* inv_freq, int rope_dim, int write_kv,
                                         const int* block_table, int max_pages, const int* positions,
                                         const int* row_seq, const int* slots, void* out, float* part_o, float* part_ml,
                                         unsigned* arrivals, int T, int H, int KV, int hd, float scale, int window,
-                                        int max_keys, int out_ld, cudaStream_t stream) {
+                                        int max_keys, int out_ld, float softcap, int sink, cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(tlc_attention_decode_fused_ok(H, KV, hd), "attention(decode, fused): %d heads, %d key/value heads of size %d are outside the kernel's range", H, KV, hd);
@@ -413,7 +419,7 @@ extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, i
 #define TLC_FM_LAUNCH(HDV, CKV, STV)                                                                                   \
   e = launch_fused<HDV, CKV, STV>(grid, passes, stream, qkv, ld, q_off, k_off, v_off, kp, vp, inv_freq, rope_dim, write_kv, \
                                 block_table, max_pages, positions, row_seq, slots, part_o, part_ml, arrivals, op, H, KV, \
-                                scale, window, n_splits, passes, out_ld)
+                                scale, window, n_splits, passes, out_ld, softcap, sink)
   if (hd == 64) TLC_FM_LAUNCH(64, 32, 4);
   else if (hd == 128) TLC_FM_LAUNCH(128, 32, 2);
   else TLC_FM_LAUNCH(256, 16, 2);

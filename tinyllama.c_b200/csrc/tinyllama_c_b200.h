@@ -183,7 +183,7 @@ int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, int k_off, i
                                const int* block_table, int max_pages, const int* positions, const int* row_seq,
                                const int* slots, void* out, float* part_o, float* part_ml, unsigned* arrivals,
                                int T, int H, int KV, int hd, float scale, int window, int max_keys, int out_ld,
-                               cudaStream_t stream);
+                               float softcap, int sink, cudaStream_t stream);
 /* Prompt rows (consecutive positions from start_pos) of a bfloat16 cache on the tensor cores. */
 int tlc_attention_prefill_ok(int dtype, int hd);
 int tlc_attention_prefill_chunks(int n_tiles_bound, int H, int max_tiles, int* chunk_tiles /* host */);

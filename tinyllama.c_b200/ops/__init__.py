@@ -71,7 +71,7 @@ _SIGNATURES = {
     "tlc_attention_decode_fused_ok": (_i, [_i, _i, _i]),
     "tlc_attention_decode_fused_passes": (_i, [_i]),
     "tlc_attention_decode_fused": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp,
-                                        _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
+                                        _vp, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _vp]),
     "tlc_attention_prefill_ok": (_i, [_i, _i]),
     "tlc_attention_prefill_chunks": (_i, [_i, _i, _i, _vp]),
     "tlc_attention_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
@@ -661,11 +661,11 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
                            v_pages: torch.Tensor, inv_freq: torch.Tensor, write_kv: bool, block_table: torch.Tensor,
                            positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
                            H: int, KV: int, hd: int, scale: float, window: int, max_keys: int,
-                           arrivals: torch.Tensor) -> None:
+                           arrivals: torch.Tensor, softcap: float = 0.0, sink: bool = False) -> None:
     """Single-token steps in one kernel: rotates the row's queries and new key (2 * len(inv_freq)
     leading dims of each head), stores the new key/value row into its page when write_kv, attends
     over the sequence's pages and writes out [T, H*hd] bfloat16.  qkv is float32 with dense rows.
-    arrivals: the caller's counters (new_arrival_counters)."""
+    arrivals: the caller's counters (new_arrival_counters).  softcap and sink as in attention()."""
     _gpu(qkv, k_pages, v_pages, inv_freq, block_table, positions, row_seq, slots, out)
     T = qkv.shape[0]
     for t, n in ((positions, "positions"), (row_seq, "row_seq"), (slots, "slots"), (block_table, "block_table")):
@@ -692,7 +692,8 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
     _call("tlc_attention_decode_fused", qkv.data_ptr(), ld, q_off, k_off, v_off, k_pages.data_ptr(), v_pages.data_ptr(),
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),
-          part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), out_ld, _stream())
+          part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), out_ld,
+          float(softcap), int(bool(sink)), _stream())
 
 
 def attention_decode_fused_passes(passes: int) -> None:
@@ -1122,7 +1123,7 @@ def qk_whole_norm(qkv: torch.Tensor, q_off: int, q_n: int, q_weight: torch.Tenso
 
 
 # ---- time mixing with a decaying matrix state -------------------------------------------------------------------
-MAX_WKV_HEAD_DIM = 256    # wkv.cu: 8 lanes a column x 32 rows a lane
+MAX_WKV_HEAD_DIM = 256    # wkv.cu: 32 lanes a column x 8 rows a lane
 
 
 def shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor) -> None:

@@ -110,14 +110,15 @@ class AttentionMixer(Part):
         """Kernels that mix() launches in a one-token step: one where the fused kernel serves (a
         bfloat16 cache, a head size it is built for, a position part with a rotation table), else
         rotation + split keys + merge."""
-        fused = self.dtype == torch.bfloat16 and self.position.rotation_table() is not None and not self._own_softmax \
+        fused = self.dtype == torch.bfloat16 and self.position.rotation_table() is not None \
             and ops.library().tlc_attention_decode_fused_ok(self.H, self.KV, self.hd) \
             and not ops.DISABLE_FUSED_DECODE_ATTENTION
         return (1 if fused else 3) + int(self.pre_transform) + int(self.gate is not None) + int(self.whole_norm is not None)
 
     @property
     def _own_softmax(self) -> bool:
-        """A capped score or a sink: served by the tcgen05 kernel of prompts, the warp kernels and the split-key kernels of single tokens."""
+        """A capped score or a sink: served by the tcgen05 kernel of prompts, the fused kernel of single tokens, the warp kernels
+        and the split-key kernels of single tokens."""
         return self.softcap > 0 or self.sink
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -187,13 +188,13 @@ class AttentionMixer(Part):
             ops.qk_rotate_norm(qkv, self.q_off, self.k_off, self.H, self.KV, self.hd, self.qk_dim, table,
                                getattr(self.position, "layout", "split_half") == "interleaved", self.qk_norm_eps, step.positions)
             table = self._no_rotation
-        if step.max_new == 1 and not self._own_softmax and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
+        if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
             att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
                                        self.H, self.KV, self.hd, self.scale, self.window or 0,
-                                       step.max_context, self._arrivals)
+                                       step.max_context, self._arrivals, self.softcap, self.sink)
             return self._gated(att, qkv)
         q = scratch_buf(f"attention.{self.cache_key}.q", (T, self.H * self.hd), self.dtype, qkv.device)
         ops.rope_kv_store(qkv, self.q_off, self.k_off, self.v_off, q, kv.k_pages, kv.v_pages, table, step.positions,
