@@ -308,6 +308,29 @@ def test_mixers_joined_by_their_own_norms(n, D):
     assert np.abs(r.cpu().numpy() - (res + y)).max() <= 1e-5 * np.abs(res + y).max()
 
 
+@pytest.mark.parametrize("T", [5, 600])
+@pytest.mark.parametrize("n,D", [(2, 256), (2, 50), (3, 64), (1, 1536)])
+@pytest.mark.parametrize("copy_dtype", ["bfloat16", "float32"])
+def test_adding_norms_leave_the_stream_in_a_second_type(T, n, D, copy_dtype):
+    """The kernels that add a normed sublayer result into the 32-bit stream also write the new rows in the type of the
+    next sublayer's input: the join of the mixers and the plain output norm, few rows and many, widths with and
+    without 16-byte rows."""
+    g = np.random.default_rng(15)
+    f32 = lambda a: np.asarray(a, dtype=np.float32).astype(np.float64)
+    parts, res = f32(g.standard_normal((T, n, D))), f32(g.standard_normal((T, D)))
+    w, outer = f32(1.0 + g.standard_normal((n, D)) * 0.2), f32(1.0 + g.standard_normal(D) * 0.2)
+    for joined in (True, False):
+        r, copy = dev(res), torch.full((T, D), 7.0, dtype=DT[copy_dtype], device="cuda")
+        if joined:
+            ops.rmsnorm_mean_add(dev(parts), dev(w), 1e-6, 1.0 / n, r, dev(outer), 1e-6, copy=copy)
+            want = res + plain.rms_norm(sum(plain.rms_norm(parts[:, i], w[i], 1e-6) for i in range(n)) / n, outer, 1e-6)
+        else:
+            ops.rmsnorm_add(dev(parts), dev(outer), 1e-6, r, copy=copy)
+            want = res + plain.rms_norm(parts.sum(axis=1), outer, 1e-6)
+        assert np.abs(r.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+        assert torch.equal(copy, r.to(DT[copy_dtype]))          # the copy is the stream itself, rounded once
+
+
 @pytest.mark.parametrize("dtype,D,F", [("bfloat16", 256, 512), ("bfloat16", 64, 40), ("bfloat16", 44, 28), ("float32", 64, 40)])
 def test_dense_feed_forward_with_both_clamps_at_work(dtype, D, F):
     g = np.random.default_rng(15)

@@ -97,6 +97,16 @@ template <> struct Out4<__nv_bfloat16> {
   }
 };
 
+// element i (or the four from i on) of a buffer whose type is known at run time
+__device__ __forceinline__ void put_as(void* p, int dtype, size_t i, float v) {
+  if (dtype == TLC_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(v);
+  else reinterpret_cast<float*>(p)[i] = v;
+}
+__device__ __forceinline__ void put4_as(void* p, int dtype, size_t i, float4 v) {
+  if (dtype == TLC_BF16) Out4<__nv_bfloat16>::put(reinterpret_cast<__nv_bfloat16*>(p) + i, v.x, v.y, v.z, v.w);
+  else Out4<float>::put(reinterpret_cast<float*>(p) + i, v.x, v.y, v.z, v.w);
+}
+
 template <typename TO, int NT, int PT>
 __global__ void __launch_bounds__(NT)
 rmsnorm_vec_kernel(const float* __restrict__ x, int x_ld, const int* __restrict__ rows, const float* __restrict__ w,
@@ -419,8 +429,8 @@ extern "C" int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu
 __global__ void __launch_bounds__(1024)
 rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ extra,
                    const float* __restrict__ gate, int gate_ld, int gate_sigmoid, const float* __restrict__ w, float eps, int D,
-                   float* __restrict__ res, int accumulate, int keep) {
-  tlc_pdl(parts, extra, gate, res);
+                   float* __restrict__ res, int accumulate, int keep, void* __restrict__ copy, int copy_dtype) {
+  tlc_pdl(parts, extra, gate, res, copy);
   __shared__ float red[33];
   extern __shared__ float yrow[];               // the summed row, where it fits (keep)
   const int t = blockIdx.x;
@@ -456,20 +466,109 @@ rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __
     }
     const float v = w ? y * s * w[d] : y;
     float* o = res + (size_t)t * D + d;
-    *o = accumulate ? *o + v : v;
+    const float r = accumulate ? *o + v : v;
+    *o = r;
+    if (copy) put_as(copy, copy_dtype, (size_t)t * D + d, r);
   }
 }
 
+// The same with a row in registers: 16-byte loads and stores, the weight fetched before the wait on the previous kernel.
+// D a multiple of 4, at most 4 * NT * PT; the sums run in the order of the kernel above.
+template <int NT, int PT>
+__global__ void __launch_bounds__(NT)
+rmsnorm_add_vec_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ extra,
+                       const float* __restrict__ gate, int gate_ld, int gate_sigmoid, const float* __restrict__ w, float eps,
+                       int D, float* __restrict__ res, int accumulate, void* __restrict__ copy, int copy_dtype) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  __shared__ float red[33];
+  const int n4 = D >> 2, t = blockIdx.x;
+  float4 wv[PT], v[PT];
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    wv[i] = (w && c < n4) ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  tlc_wait(parts, extra, gate, res, copy);
+  const float4* pr = reinterpret_cast<const float4*>(parts + (size_t)t * n_parts * D);
+  for (int p = 0; p < n_parts; p++) {
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+      const int c = threadIdx.x + i * NT;
+      if (c < n4) {
+        const float4 a = pr[(size_t)p * n4 + c];
+        v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+      }
+    }
+  }
+  if (extra) {
+    float g = 1.0f;
+    if (gate) {
+      g = gate[(size_t)t * gate_ld];
+      if (gate_sigmoid) g = 1.0f / (1.0f + expf(-g));
+    }
+    const float4* er = reinterpret_cast<const float4*>(extra + (size_t)t * D);
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+      const int c = threadIdx.x + i * NT;
+      if (c < n4) {
+        const float4 a = er[c];
+        v[i].x = fmaf(g, a.x, v[i].x); v[i].y = fmaf(g, a.y, v[i].y); v[i].z = fmaf(g, a.z, v[i].z); v[i].w = fmaf(g, a.w, v[i].w);
+      }
+    }
+  }
+  float4 r[PT];
+  float4* rr = reinterpret_cast<float4*>(res + (size_t)t * D);
+#pragma unroll
+  for (int i = 0; i < PT; i++) {                           // in flight during the block's sum
+    const int c = threadIdx.x + i * NT;
+    r[i] = (accumulate && c < n4) ? rr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float s = 1.0f;
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PT; i++) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = block_sum(ss, red);
+    s = 1.0f / sqrtf(ss / (float)D + eps);
+  }
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    if (c >= n4) continue;
+    if (w) {
+      r[i].x += v[i].x * s * wv[i].x; r[i].y += v[i].y * s * wv[i].y; r[i].z += v[i].z * s * wv[i].z; r[i].w += v[i].w * s * wv[i].w;
+    } else {
+      r[i].x += v[i].x; r[i].y += v[i].y; r[i].z += v[i].z; r[i].w += v[i].w;
+    }
+    rr[c] = r[i];
+    if (copy) put4_as(copy, copy_dtype, (size_t)t * D + 4 * c, r[i]);
+  }
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p % 16) == 0; }
+
 extern "C" int tlc_rmsnorm_add(const float* parts, int n_parts, const float* extra, const float* gate, int gate_ld,
                                int gate_sigmoid, const float* w, float eps, int T, int D, float* res, int accumulate,
-                               cudaStream_t stream) {
+                               void* copy, int copy_dtype, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(n_parts >= 0 && (n_parts > 0 || extra != nullptr), "rmsnorm_add: nothing to add");
+  TLC_REQUIRE(copy == nullptr || copy_dtype == TLC_F32 || copy_dtype == TLC_BF16, "rmsnorm_add: unknown dtype code %d of the copy", copy_dtype);
+  if (D % 4 == 0 && D <= 16384 && aligned16(parts) && aligned16(extra) && aligned16(w) && aligned16(res) && aligned16(copy)) {
+    const int n4 = D / 4;
+#define TLC_RA_LAUNCH(NT, PT)                                                                                             \
+  tlc_launch(rmsnorm_add_vec_kernel<NT, PT>, dim3(T), dim3(NT), 0, stream, parts, n_parts, extra, gate, gate_ld, gate_sigmoid, w, \
+             eps, D, res, accumulate, copy, copy_dtype)
+    if (T >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_RA_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_RA_LAUNCH) }
+#undef TLC_RA_LAUNCH
+    TLC_CHECK_LAUNCH("rmsnorm_add");
+    return 0;
+  }
   const int keep = (size_t)D * sizeof(float) <= 40 * 1024;
   // few rows (single-token steps): more threads a row, so that a thread's loads are few and in flight together
   const int nt = (T < 256 && D >= 1024) ? 1024 : 256;
   tlc_launch(rmsnorm_add_kernel, dim3(T), dim3(nt), keep ? (size_t)D * sizeof(float) : 0, stream, parts, n_parts, extra, gate, gate_ld,
-             gate_sigmoid, w, eps, D, res, accumulate, keep);
+             gate_sigmoid, w, eps, D, res, accumulate, keep, copy, copy_dtype);
   TLC_CHECK_LAUNCH("rmsnorm_add");
   return 0;
 }
@@ -532,8 +631,9 @@ extern "C" int tlc_softcap(float* x, long long n, float cap, cudaStream_t stream
 #define MEAN_MAX_PARTS 8
 __global__ void __launch_bounds__(1024)
 rmsnorm_mean_add_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ w, float eps, float scale,
-                        const float* __restrict__ wo, float eps_o, int D, float* __restrict__ res, int accumulate, int keep) {
-  tlc_pdl(parts, res);
+                        const float* __restrict__ wo, float eps_o, int D, float* __restrict__ res, int accumulate, int keep,
+                        void* __restrict__ copy, int copy_dtype) {
+  tlc_pdl(parts, res, copy);
   __shared__ float red[33];
   extern __shared__ float yrow[];
   const int t = blockIdx.x;
@@ -571,17 +671,107 @@ rmsnorm_mean_add_kernel(const float* __restrict__ parts, int n_parts, const floa
     const float y = (wo && keep) ? yrow[d] : mean_at(d);          // (yrow[d] was written by this thread)
     const float v = wo ? y * s * wo[d] : y;
     float* o = res + (size_t)t * D + d;
-    *o = accumulate ? *o + v : v;
+    const float r = accumulate ? *o + v : v;
+    *o = r;
+    if (copy) put_as(copy, copy_dtype, (size_t)t * D + d, r);
+  }
+}
+
+// Two summands with both rows in registers: 16-byte loads and stores, the two sums of squares in one pass over the
+// block.  D a multiple of 4, at most 4 * NT * PT.
+template <int NT, int PT>
+__global__ void __launch_bounds__(NT)
+rmsnorm_mean2_add_vec_kernel(const float* __restrict__ parts, const float* __restrict__ w, float eps, float scale,
+                             const float* __restrict__ wo, float eps_o, int D, float* __restrict__ res, int accumulate,
+                             void* __restrict__ copy, int copy_dtype) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  __shared__ float red[2][33];
+  const int n4 = D >> 2, t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float4 w0[PT], w1[PT], a[PT], b[PT];
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    w0[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    w1[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(w) + n4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  tlc_wait(parts, res, copy);
+  const float4* pr = reinterpret_cast<const float4*>(parts + (size_t)t * 2 * D);
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    a[i] = c < n4 ? pr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    b[i] = c < n4 ? pr[n4 + c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float sa = 0.f, sb = 0.f;
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    sa += a[i].x * a[i].x + a[i].y * a[i].y + a[i].z * a[i].z + a[i].w * a[i].w;
+    sb += b[i].x * b[i].x + b[i].y * b[i].y + b[i].z * b[i].z + b[i].w * b[i].w;
+  }
+  sa = warp_sum(sa);
+  sb = warp_sum(sb);
+  if (lane == 0) { red[0][warp] = sa; red[1][warp] = sb; }
+  __syncthreads();
+  if (warp < 2) {
+    float x = lane < NT / 32 ? red[warp][lane] : 0.f;
+    x = warp_sum(x);
+    if (lane == 0) red[warp][32] = x;
+  }
+  __syncthreads();
+  const float ia = scale / sqrtf(red[0][32] / (float)D + eps), ib = scale / sqrtf(red[1][32] / (float)D + eps);
+  float4 y[PT], r[PT];
+  float4* rr = reinterpret_cast<float4*>(res + (size_t)t * D);
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    r[i] = (accumulate && c < n4) ? rr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    y[i].x = fmaf(b[i].x * ib, w1[i].x, fmaf(a[i].x * ia, w0[i].x, 0.f));
+    y[i].y = fmaf(b[i].y * ib, w1[i].y, fmaf(a[i].y * ia, w0[i].y, 0.f));
+    y[i].z = fmaf(b[i].z * ib, w1[i].z, fmaf(a[i].z * ia, w0[i].z, 0.f));
+    y[i].w = fmaf(b[i].w * ib, w1[i].w, fmaf(a[i].w * ia, w0[i].w, 0.f));
+  }
+  float s = 1.0f;
+  if (wo) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PT; i++) ss += y[i].x * y[i].x + y[i].y * y[i].y + y[i].z * y[i].z + y[i].w * y[i].w;
+    ss = block_sum(ss, red[0]);
+    s = 1.0f / sqrtf(ss / (float)D + eps_o);
+  }
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    if (c >= n4) continue;
+    if (wo) {
+      const float4 o = __ldg(reinterpret_cast<const float4*>(wo) + c);
+      r[i].x += y[i].x * s * o.x; r[i].y += y[i].y * s * o.y; r[i].z += y[i].z * s * o.z; r[i].w += y[i].w * s * o.w;
+    } else {
+      r[i].x += y[i].x; r[i].y += y[i].y; r[i].z += y[i].z; r[i].w += y[i].w;
+    }
+    rr[c] = r[i];
+    if (copy) put4_as(copy, copy_dtype, (size_t)t * D + 4 * c, r[i]);
   }
 }
 extern "C" int tlc_rmsnorm_mean_add(const float* parts, int n_parts, const float* w, float eps, float scale, const float* wo,
-                                    float eps_o, int T, int D, float* res, int accumulate, cudaStream_t stream) {
+                                    float eps_o, int T, int D, float* res, int accumulate, void* copy, int copy_dtype,
+                                    cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(n_parts >= 1 && n_parts <= MEAN_MAX_PARTS, "rmsnorm_mean_add: %d summands (1..%d)", n_parts, MEAN_MAX_PARTS);
+  TLC_REQUIRE(copy == nullptr || copy_dtype == TLC_F32 || copy_dtype == TLC_BF16, "rmsnorm_mean_add: unknown dtype code %d of the copy", copy_dtype);
+  if (n_parts == 2 && D % 4 == 0 && D <= 16384 && aligned16(parts) && aligned16(w) && aligned16(wo) && aligned16(res) && aligned16(copy)) {
+    const int n4 = D / 4;
+#define TLC_RM_LAUNCH(NT, PT)                                                                                           \
+  tlc_launch(rmsnorm_mean2_add_vec_kernel<NT, PT>, dim3(T), dim3(NT), 0, stream, parts, w, eps, scale, wo, eps_o, D, res, accumulate, \
+             copy, copy_dtype)
+    if (T >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_RM_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_RM_LAUNCH) }
+#undef TLC_RM_LAUNCH
+    TLC_CHECK_LAUNCH("rmsnorm_mean_add");
+    return 0;
+  }
   const int keep = (size_t)D * sizeof(float) <= 40 * 1024;
   const int nt = (T < 256 && D >= 1024) ? 1024 : 256;
   tlc_launch(rmsnorm_mean_add_kernel, dim3(T), dim3(nt), keep ? (size_t)D * sizeof(float) : 0, stream, parts, n_parts, w, eps, scale, wo,
-             eps_o, D, res, accumulate, keep);
+             eps_o, D, res, accumulate, keep, copy, copy_dtype);
   TLC_CHECK_LAUNCH("rmsnorm_mean_add");
   return 0;
 }

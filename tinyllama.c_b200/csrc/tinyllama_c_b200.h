@@ -93,9 +93,11 @@ int tlc_convert(const float* x, int ldx, int T, int D, void* out, int dtype, int
 int tlc_softcap(float* x, long long n, float cap, cudaStream_t stream);
 /* The mean of several sublayers' results, each normed by itself: y = scale * sum_p parts[t, p, :] / rms(parts[t, p, :]) *
  * w[p, :] (parts float [T, n_parts, D], w float [n_parts, D], rms with eps inside the root); then res[t] (+)= y, or with
- * an outer weight wo [D]: res[t] (+)= y / rms(y; eps_o) * wo. */
+ * an outer weight wo [D]: res[t] (+)= y / rms(y; eps_o) * wo.  copy (or NULL): [T, D] of type copy_dtype that receives
+ * the new res as well. */
 int tlc_rmsnorm_mean_add(const float* parts, int n_parts, const float* w, float eps, float scale, const float* wo,
-                         float eps_o, int T, int D, float* res, int accumulate, cudaStream_t stream);
+                         float eps_o, int T, int D, float* res, int accumulate, void* copy, int copy_dtype,
+                         cudaStream_t stream);
 /* RMSNorm with token shift: n[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w and out[t] = n[t] + (n[t-1] - n[t]) * mu, with
  * n[t-1] the normed row of the sequence's previous token: the row above in this step, or what the sequence's slot of
  * state [n_slots, D] holds from its last step (zeros at position 0).  The slot then receives the sequence's last normed
@@ -105,10 +107,11 @@ int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu, float eps
                       int out_dtype, cudaStream_t stream);
 /* res[t] (+)= y[t] / sqrt(mean(y[t]^2) + eps) * w (w NULL: y[t] itself) with y[t] = sum over p < n_parts of
  * parts[t, p, :] + g[t] * extra[t, :]; parts float [T, n_parts, D] (NULL with n_parts 0), extra float [T, D] or NULL,
- * g[t] = gate[t * gate_ld] (its sigmoid with gate_sigmoid; 1 with gate NULL), res float [T, D]. */
+ * g[t] = gate[t * gate_ld] (its sigmoid with gate_sigmoid; 1 with gate NULL), res float [T, D].  copy (or NULL): [T, D]
+ * of type copy_dtype that receives the new res as well. */
 int tlc_rmsnorm_add(const float* parts, int n_parts, const float* extra, const float* gate, int gate_ld,
                     int gate_sigmoid, const float* w, float eps, int T, int D, float* res, int accumulate,
-                    cudaStream_t stream);
+                    void* copy, int copy_dtype, cudaStream_t stream);
 
 /* ---- linear layers (gemm_tcgen05.cu, gemm_simt.cu) ----------------------------------------------------
  * out[m, n] (+)= (sum_k a[m, k] w[n, k]) * colscale[n] + colbias[n];  a [M, K], w [N, K], 32-bit sums.

@@ -120,9 +120,11 @@ class Model:
         x = torch.empty((step.n_rows, self.hidden), dtype=torch.float32, device=self.device)
         ops.embed(step.tokens, self.embed_table, self.embed_scale, x)
         with step_scratch(step):                       # the layers share the step's temporaries
+            ready = False                              # whether a layer left the stream in the activation type for the next
             for r, run in enumerate(self.schedule):
-                self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes,
-                                                                         run.kv_cache))
+                wanted = r + 1 < len(self.schedule) and self.layers[self.schedule[r + 1].layer].reads_stream_copy
+                ready = self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes,
+                                                                                 run.kv_cache), ready, wanted)
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()

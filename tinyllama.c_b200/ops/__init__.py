@@ -94,13 +94,13 @@ _SIGNATURES = {
     "tlc_glu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),
     "tlc_convert": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp]),
     "tlc_softcap": (_i, [_vp, _ll, _f, _vp]),
-    "tlc_rmsnorm_mean_add": (_i, [_vp, _i, _vp, _f, _f, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_rmsnorm_mean_add": (_i, [_vp, _i, _vp, _f, _f, _vp, _f, _i, _i, _vp, _i, _vp, _i, _vp]),
     "tlc_qk_whole_norm": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _f, _i, _vp]),
     "tlc_shift_mix": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "tlc_wkv_scan": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "tlc_moe_identity": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "tlc_rmsnorm_shift": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
-    "tlc_rmsnorm_add": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_rmsnorm_add": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _f, _i, _i, _vp, _i, _vp, _i, _vp]),
     "tlc_latent_prepare": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i,
                                 _i, _i, _vp]),
     "tlc_latent_attention": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
@@ -352,10 +352,12 @@ def softcap(x: torch.Tensor, cap: float) -> None:
 
 
 def rmsnorm_mean_add(parts: torch.Tensor, weights: torch.Tensor, eps: float, scale: float, residual: torch.Tensor,
-                     outer_weight: Optional[torch.Tensor] = None, outer_eps: float = 0.0, accumulate: bool = True) -> None:
+                     outer_weight: Optional[torch.Tensor] = None, outer_eps: float = 0.0, accumulate: bool = True,
+                     copy: Optional[torch.Tensor] = None) -> None:
     """y = scale * sum_p rmsnorm(parts[:, p, :]) * weights[p]  (parts float32 [T, n, D], weights float32 [n, D]); then
-    residual (+)= y, or with an outer weight [D] residual (+)= rmsnorm(y; outer_eps) * outer_weight."""
-    _gpu(parts, weights, residual, outer_weight)
+    residual (+)= y, or with an outer weight [D] residual (+)= rmsnorm(y; outer_eps) * outer_weight.  copy [T, D] (float32
+    or bfloat16, contiguous) receives the new residual rows as well."""
+    _gpu(parts, weights, residual, outer_weight, copy)
     T, n, D = parts.shape
     if parts.dtype != torch.float32 or not parts.is_contiguous() or residual.dtype != torch.float32 \
             or not residual.is_contiguous() or tuple(residual.shape) != (T, D):
@@ -363,7 +365,7 @@ def rmsnorm_mean_add(parts: torch.Tensor, weights: torch.Tensor, eps: float, sca
     _f32vec(weights, n * D, "rmsnorm_mean_add weights")
     _f32vec(outer_weight, D, "rmsnorm_mean_add outer weight")
     _call("tlc_rmsnorm_mean_add", parts.data_ptr(), n, weights.data_ptr(), float(eps), float(scale), _p(outer_weight),
-          float(outer_eps), T, D, residual.data_ptr(), int(bool(accumulate)), _stream())
+          float(outer_eps), T, D, residual.data_ptr(), int(bool(accumulate)), *_copy_of(copy, T, D, "rmsnorm_mean_add"), _stream())
 
 
 def rmsnorm_shift(x: torch.Tensor, weight: torch.Tensor, mix: torch.Tensor, eps: float, state: torch.Tensor, step,
@@ -386,11 +388,12 @@ def rmsnorm_shift(x: torch.Tensor, weight: torch.Tensor, mix: torch.Tensor, eps:
 
 def rmsnorm_add(parts: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, residual: torch.Tensor,
                 extra: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_sigmoid: bool = False,
-                accumulate: bool = True) -> None:
+                accumulate: bool = True, copy: Optional[torch.Tensor] = None) -> None:
     """residual[t] (+)= rmsnorm(y[t]) * weight (weight None: y[t] itself) with y[t] = sum_p parts[t, p, :] + g[t] *
     extra[t, :]; parts float32 [T, D] or [T, n, D], extra float32 [T, D], gate float32 [T] or one column of a wider
-    float32 matrix; g is the gate, or its sigmoid."""
-    _gpu(parts, weight, residual, extra, gate)
+    float32 matrix; g is the gate, or its sigmoid.  copy [T, D] (float32 or bfloat16, contiguous) receives the new
+    residual rows as well."""
+    _gpu(parts, weight, residual, extra, gate, copy)
     T, D = residual.shape
     n = 0
     if parts is not None:
@@ -408,7 +411,16 @@ def rmsnorm_add(parts: Optional[torch.Tensor], weight: Optional[torch.Tensor], e
         raise KernelError("rmsnorm_add: the residual stream must be contiguous float32")
     _f32vec(weight, D, "rmsnorm_add weight")
     _call("tlc_rmsnorm_add", _p(parts), n, _p(extra), _p(gate), int(gate_ld), int(bool(gate_sigmoid)), _p(weight), float(eps),
-          T, D, residual.data_ptr(), int(bool(accumulate)), _stream())
+          T, D, residual.data_ptr(), int(bool(accumulate)), *_copy_of(copy, T, D, "rmsnorm_add"), _stream())
+
+
+def _copy_of(copy: Optional[torch.Tensor], T: int, D: int, what: str):
+    """Pointer and type code of the optional second output of the kernels that add into the residual stream."""
+    if copy is None:
+        return None, 0
+    if tuple(copy.shape) != (T, D) or not copy.is_contiguous():
+        raise KernelError(f"{what}: the copy must be contiguous {(T, D)}")
+    return copy.data_ptr(), dtype_code(copy.dtype)
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

@@ -270,6 +270,11 @@ class step_scratch:
         return False
 
 
+def scratch_is_shared() -> bool:
+    """Whether a step is running, so that scratch_buf() returns the same buffer for the same (tag, shape, type)."""
+    return _scratch is not None
+
+
 def scratch_buf(tag: str, shape, dtype: torch.dtype, device) -> torch.Tensor:
     """An uninitialised buffer for a temporary of the running step; the same one for the same (tag, shape, type)
     until the step ends.  Outside a step it is a plain allocation."""

@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty, scratch_buf
+from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty, scratch_buf, scratch_is_shared
 from .linear import StackedLinear
 
 
@@ -250,7 +250,7 @@ class Block(Part):
         main.wait_event(self._ffn_done)
         self.ffn.add_parts(terms, x32)
 
-    def _joined_mixers(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
+    def _joined_mixers(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache, copy: Optional[torch.Tensor] = None) -> None:
         """x <- x + out_norm(join(mixer_i(h))): every mixer's result in rows of its own, then the join (and the norm after
         it) in one kernel.  Mixers that offer their projections share the input product and, in one-token steps, run side
         by side on streams."""
@@ -272,20 +272,54 @@ class Block(Part):
                 if not self._mixer_overwrites[i]:
                     raise ValueError("a layer that joins its mixers' results needs mixers whose forward() can overwrite its target")
                 m.forward(x32 if reads[i] else normed, step, cache, outs[:, i], accumulate=False)
-        self.mixer_join.add_joined(outs, x32, self.mixer_out_norm)
+        self.mixer_join.add_joined(outs, x32, self.mixer_out_norm, copy=copy)
+
+    # A sublayer without a norm in front reads the residual stream in the activation type.  The kernel that last added
+    # into the stream (an output norm) writes that copy as its second output, so that no kernel of its own has to make it:
+    # _stream_copy() names the buffer to the adding kernel and notes that it is filled, _pre_norm() then hands it over.
+    @property
+    def reads_stream_copy(self) -> bool:
+        """Whether this layer's first step is a copy of the residual stream in the activation type (no norm before the
+        mixers, and a mixer that does not take the 32-bit rows themselves)."""
+        return bool(self.mixers) and self._plain_copy(self.mixer_norm) \
+            and not all(bool(getattr(m, "reads_stream", False)) for m in self.mixers)
+
+    @staticmethod
+    def _plain_copy(norm) -> bool:
+        return norm is not None and getattr(norm, "identity", False) and not hasattr(norm, "forward_step")
+
+    def _stream_copy(self, tag: str, x32: torch.Tensor) -> Optional[torch.Tensor]:
+        if not (x32.is_cuda and scratch_is_shared()):
+            return None
+        self._copied.add(tag)
+        return scratch_buf(tag, x32.shape, self.dtype, x32.device)
 
     def _pre_norm(self, norm, x32: torch.Tensor, tag: str, step: StepInfo, cache: LayerCache) -> torch.Tensor:
         normed = scratch_buf(tag, x32.shape, self.dtype, x32.device)
+        if tag in self._copied:                       # filled by the kernel that last added into the stream
+            self._copied.discard(tag)
+            return normed
         if hasattr(norm, "forward_step"):             # a norm with per-sequence state (token shift)
             norm.forward_step(x32, normed, step, cache)
         else:
             norm.forward(x32, normed)
         return normed
 
-    def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
-        """Updates the float32 residual stream x32 [T, D] in place."""
+    def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache, copy_ready: bool = False,
+                copy_for_next: bool = False) -> bool:
+        """Updates the float32 residual stream x32 [T, D] in place.  copy_ready: the layer before has left the stream in
+        the activation type where this layer's mixers look for it; copy_for_next: the next layer wants the same of this
+        one.  Returns whether that copy was written."""
+        self._copied = {"block.normed"} if copy_ready and self.reads_stream_copy and scratch_is_shared() else set()
+        last_add_is_mixers = self.ffn is None or self.parallel_ffn
+        copy = None
+        if self.mixers and self.mixer_out_norm is not None:
+            if last_add_is_mixers:
+                copy = self._stream_copy("block.normed", x32) if copy_for_next and self.ffn is None else None
+            elif self._plain_copy(self.ffn_norm):
+                copy = self._stream_copy("block.ffn_normed", x32)
         if self.mixers and self.mixer_join is not None:
-            self._joined_mixers(x32, step, cache)
+            self._joined_mixers(x32, step, cache, copy)
         elif self.mixers and self.mixer_out_norm is not None:
             # x <- x + out_norm(sum of the mixers' outputs); a mixer that reads the stream itself gets the 32-bit rows
             reads = [bool(getattr(m, "reads_stream", False)) and getattr(self.mixer_norm, "identity", False) for m in self.mixers]
@@ -298,18 +332,20 @@ class Block(Part):
                     m.forward(x32 if reads[i] else normed, step, cache, y, accumulate=i > 0)
                 else:
                     m.forward(x32 if reads[i] else normed, step, cache, y)
-            self.mixer_out_norm.add_normed(y, x32)
+            self.mixer_out_norm.add_normed(y, x32, copy=copy)
         elif self.mixers:
             normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
             if self._beside(x32, step):
                 self._two_branches(normed, x32, lambda: self._run_mixers(normed, x32, step, cache))
-                return
+                return False
             self._run_mixers(normed, x32, step, cache)
         if self.parallel_ffn:
             # h was normed before the mixers added anything; the sum x + mixers(h) + ffn(h) forms in the residual stream
             self.ffn.forward(normed, x32)
-        elif self.ffn is not None:
-            self._feed_forward(x32, step, cache)
+            return False
+        if self.ffn is not None:
+            return self._feed_forward(x32, step, cache, copy_for_next)
+        return copy is not None
 
     def _run_mixers(self, normed: torch.Tensor, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """The mixers of a layer without a mixer output norm, from their shared normed input into the residual stream."""
@@ -331,9 +367,12 @@ class Block(Part):
             for m in self.mixers:
                 m.forward(normed, step, cache, x32)
 
-    def _feed_forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
-        """A feed-forward with a norm of its own, after the mixers."""
+    def _feed_forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache, copy_for_next: bool = False) -> bool:
+        """A feed-forward with a norm of its own, after the mixers.  Returns whether the kernel that added its result
+        also left the stream in the activation type for the next layer (copy_for_next)."""
         normed = self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache)
+        copy = self._stream_copy("block.normed", x32) if copy_for_next and self.ffn_out_norm is not None else None
+        self._copied.discard("block.normed")          # (the next layer is told by the return value)
         # without a norm in front, a feed-forward that can use them (takes_stream) also gets the 32-bit rows themselves
         more = {"stream": x32} if getattr(self.ffn_norm, "identity", False) and getattr(self.ffn, "takes_stream", False) else {}
         if self.ffn_out_norm is None:
@@ -341,7 +380,7 @@ class Block(Part):
         elif hasattr(self.ffn, "forward_parts"):
             # a feed-forward whose result is a sum of terms hands them to the norm, which adds them up itself
             parts, extra, gate = self.ffn.forward_parts(normed, **more)
-            self.ffn_out_norm.add_normed(parts, x32, extra, gate)
+            self.ffn_out_norm.add_normed(parts, x32, extra, gate, copy=copy)
         else:
             y = scratch_buf("block.ffn_out", x32.shape, torch.float32, x32.device)
             if self._ffn_overwrites:
@@ -349,4 +388,5 @@ class Block(Part):
             else:
                 y.zero_()
                 self.ffn.forward(normed, y)
-            self.ffn_out_norm.add_normed(y, x32)
+            self.ffn_out_norm.add_normed(y, x32, copy=copy)
+        return copy is not None

@@ -34,10 +34,11 @@ class RMSNorm(Part):
         return out
 
     def add_normed(self, parts: Optional[torch.Tensor], residual: torch.Tensor, extra: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None) -> None:
+                   gate: Optional[torch.Tensor] = None, copy: Optional[torch.Tensor] = None) -> None:
         """As a sublayer's output norm: residual += norm(y) with y = the sum of parts [T, (n,) D] (+ sigmoid(gate[t]) *
-        extra[t], gate being a logit per row)."""
-        ops.rmsnorm_add(parts, self.weight, self.eps, residual, extra, gate, gate_sigmoid=True)
+        extra[t], gate being a logit per row).  copy [T, D]: receives the new residual rows in its own type (what the
+        next sublayer reads where it has no norm in front)."""
+        ops.rmsnorm_add(parts, self.weight, self.eps, residual, extra, gate, gate_sigmoid=True, copy=copy)
 
 
 @register_norm("rmsnorm_shift")
@@ -107,9 +108,11 @@ class RMSNormMean(Part):
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         self.weights = torch.stack([to_vec(tensors[n], device) for n in self.weight_names]).contiguous()
 
-    def add_joined(self, parts: torch.Tensor, residual: torch.Tensor, out_norm: Optional[RMSNorm] = None) -> None:
-        """parts float32 [T, n, D]: the mixers' results side by side."""
+    def add_joined(self, parts: torch.Tensor, residual: torch.Tensor, out_norm: Optional[RMSNorm] = None,
+                   copy: Optional[torch.Tensor] = None) -> None:
+        """parts float32 [T, n, D]: the mixers' results side by side.  copy [T, D]: receives the new residual rows in its
+        own type."""
         if out_norm is not None and type(out_norm) is not RMSNorm:
             raise ValueError("rmsnorm_mean: the norm after the join must be a plain RMS norm")
         ops.rmsnorm_mean_add(parts, self.weights, self.eps, self.scale, residual,
-                             None if out_norm is None else out_norm.weight, 0.0 if out_norm is None else out_norm.eps)
+                             None if out_norm is None else out_norm.weight, 0.0 if out_norm is None else out_norm.eps, copy=copy)
