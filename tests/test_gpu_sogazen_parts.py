@@ -262,7 +262,7 @@ def test_wkv_mixer_with_its_mixes_gate_and_norm(dtype, H, d, R):
     """The whole mixer: five mixes with the previous token's input (kept across steps, zeros at position 0), the decay's
     two small products, the scan, each head divided by its root mean square, the weight, the gate, the output."""
     g = np.random.default_rng(13)
-    D, HD = 44, H * d
+    D, HD = (128 if d == 64 else 44), H * d        # 128: rows of 16-byte multiples, which the tiled product of prompts takes
     names = {k: "w." + k for k in ("r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o")}
     names.update({"mu_" + s: "w.mu." + s for s in ("r", "k", "v", "g", "w")})
     W = {"w." + s: draw(g, (HD, D), 0.25, dtype) for s in ("r", "k", "v", "g")}

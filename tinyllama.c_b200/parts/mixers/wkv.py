@@ -27,6 +27,7 @@ from ..linear import StackedLinear, matrix_dtype
 class WKVMixer(Part):
     reads_stream = True        # forward() takes the 32-bit input rows, not a copy in the activation type
     MIXES = ("r", "k", "v", "g", "w")
+    TILED_FROM_ROWS = 256      # steps of this many rows run r, k, v, g as four products of the tiled kernel
 
     def __init__(self, hidden: int, n_heads: int, head_dim: int, eps: float, names: Dict[str, str], cache_key: str = "wkv",
                  decay_rank: Optional[int] = None):
@@ -90,7 +91,12 @@ class WKVMixer(Part):
         ops.shift_mix(x32, self.mu, cache.state[self.cache_key + ".shift"], step, mixes)
         flat = mixes.view(T, 5 * D)
         rkvg = new("rkvg", (T, 4 * HD), torch.float32)
-        ops.linear_heads(flat, D, self.w_rkvg, rkvg, HD)                       # groups r, k, v, g: one product each
+        if T >= self.TILED_FROM_ROWS and self.act_dtype == torch.bfloat16:
+            # prompts: each of r, k, v, g is a full-size product of its own mix, so each takes the tiled tensor-core kernel
+            for i in range(4):
+                ops.linear(flat[:, i * D:(i + 1) * D], self.w_rkvg[i], rkvg[:, i * HD:(i + 1) * HD])
+        else:
+            ops.linear_heads(flat, D, self.w_rkvg, rkvg, HD)                   # groups r, k, v, g: one launch for the four
         hidden = new("decay_hidden", (T, self.decay_rank), torch.float32)
         ops.linear(flat[:, 4 * D:], self.w1, hidden)
         hidden_act = new("decay_act", (T, self.decay_rank), self.act_dtype)
