@@ -297,6 +297,44 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
   }
 }
 
+// Groups of at most 32 float4 (a head of up to 128 values): a warp per group, eight groups a block, the sum by shuffles
+// alone.  The shape follows from the group's width alone, so a group's sum has the same tree in every step.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_warp_kernel(const float* __restrict__ y, const float* __restrict__ y2, const float* __restrict__ z, int ldz,
+                          const float* __restrict__ w, float eps, long long n_rows, int n_groups, int Di, int gs,
+                          int norm_before_gate, TO* __restrict__ out, int out_ld, float out_scale) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  const long long idx = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, n4 = gs >> 2;
+  const bool on = idx < n_rows && lane < n4;
+  const long long t = idx / n_groups;
+  const int g = (int)(idx % n_groups);
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 wv = on ? __ldg(reinterpret_cast<const float4*>(w + (size_t)g * gs) + lane) : zero;
+  tlc_wait(y, y2, z, out);
+  float4 v = zero, gate = zero;
+  if (on) {
+    v = reinterpret_cast<const float4*>(y + (size_t)t * Di + (size_t)g * gs)[lane];
+    gate = reinterpret_cast<const float4*>(z + (size_t)t * ldz + (size_t)g * gs)[lane];
+    if (y2 != nullptr) {
+      const float4 u = reinterpret_cast<const float4*>(y2 + (size_t)t * Di + (size_t)g * gs)[lane];
+      v = make_float4(v.x + u.x, v.y + u.y, v.z + u.z, v.w + u.w);
+    }
+  }
+  constexpr bool QUICK = sizeof(TO) == 2;                // a bfloat16 output means a bfloat16 run
+  gate = make_float4(silu_of<QUICK>(gate.x), silu_of<QUICK>(gate.y), silu_of<QUICK>(gate.z), silu_of<QUICK>(gate.w));
+  if (!norm_before_gate) { v.x *= gate.x; v.y *= gate.y; v.z *= gate.z; v.w *= gate.w; }
+  const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+  const float s = out_scale / sqrtf(ss / (float)gs + eps);
+  if (!on) return;
+  TO* o = out + (size_t)t * out_ld + (size_t)g * gs + 4 * lane;
+  if (norm_before_gate)
+    Out4<TO>::put(o, (v.x * s * wv.x) * gate.x, (v.y * s * wv.y) * gate.y, (v.z * s * wv.z) * gate.z, (v.w * s * wv.w) * gate.w);
+  else
+    Out4<TO>::put(o, v.x * s * wv.x, v.y * s * wv.y, v.z * s * wv.z, v.w * s * wv.w);
+}
+
 extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
                                  int Di, int n_groups, int norm_before_gate, void* out, int out_dtype, int out_ld,
                                  float out_scale, cudaStream_t stream) {
@@ -309,6 +347,14 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z,
       ((uintptr_t)z % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0 && out_ld % 4 == 0 &&
       ((uintptr_t)y2 % 16) == 0) {
     const int n4 = gs / 4;
+    if (n4 <= 32) {
+      const long long n_rows = (long long)T * n_groups;
+      TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_warp_kernel<TO>, dim3((unsigned)((n_rows + 7) / 8)), dim3(256), 0, stream,
+                                                   y, y2, (const float*)z, ldz, w, eps, n_rows, n_groups, Di, gs, norm_before_gate,
+                                                   (TO*)out, out_ld, out_scale));
+      TLC_CHECK_LAUNCH("gated_rmsnorm");
+      return 0;
+    }
 #define TLC_GRMS_LAUNCH(NT, PT)                                                                                         \
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y, y2,    \
                                                (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale))
