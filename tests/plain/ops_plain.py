@@ -119,7 +119,8 @@ def rope_kv_store(qkv, q_off, k_off, v_off, q_out, k_pages, v_pages, inv_freq, p
 
 
 def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, H, KV, hd, scale, window=0,
-              decode_max_keys=0, cu_seqlens=None, start_pos=None, max_keys=0, max_blocks=0, key_ranges=0, softcap=0.0, sink=False):
+              decode_max_keys=0, cu_seqlens=None, start_pos=None, max_keys=0, max_blocks=0, key_ranges=0, softcap=0.0, sink=False,
+              keep_first=0, sink_values=None):
     T = q.shape[0]
     res = torch.zeros((T, H, hd), dtype=torch.float64)
     qf = _f(q).reshape(T, H, hd)
@@ -129,6 +130,8 @@ def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, 
         n_keys = p + 1
         start = n_keys - window if (window and n_keys > window) else 0
         idx = torch.arange(start, n_keys)
+        if window and keep_first and start > 0:                     # the sequence's first keys stay visible
+            idx = torch.cat([torch.arange(0, min(keep_first, start)), idx])
         pages = table[(idx // PAGE).long()].long()
         K = _f(k_pages[pages, :, (idx % PAGE).long(), :])          # [n, KV, hd]
         V = _f(v_pages[pages, :, (idx % PAGE).long(), :])
@@ -137,8 +140,9 @@ def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, 
             sc = (K[:, g] @ qf[t, h]) * scale
             if softcap:
                 sc = softcap * torch.tanh(sc / softcap)
-            if sink:            # one more term of score 0 in the denominator, with no value
-                pr = torch.softmax(torch.cat([sc, sc.new_zeros(1)]), dim=0)[:-1]
+            if sink or sink_values is not None:   # one more term (score 0, or the head's own) in the denominator, with no value
+                sv = sc.new_zeros(1) if sink_values is None else _f(sink_values[h]).reshape(1)
+                pr = torch.softmax(torch.cat([sc, sv]), dim=0)[:-1]
             else:
                 pr = torch.softmax(sc, dim=0)
             res[t, h] = pr @ V[:, g]

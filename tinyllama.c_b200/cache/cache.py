@@ -11,7 +11,7 @@ one by one (graph.c:343-357; falcon_h1.c:136-147) and serves one sequence per se
 * layers whose mixers ask for keys/values with the same (kv heads, head size, window) form
   a *group* with one page pool [layers, pages, kv heads, 64, head size] and one block
   table [slots, pages per slot]; a windowed group gives back pages that fell out of every
-  future query's window;
+  future query's window (except those that hold the first positions a request says stay visible);
 * every fixed-size state request (same key and shape) forms a group [layers, slots, *shape];
   a sequence at position 0 is treated as all-zero by the kernels, so nothing is cleared
   on reuse.
@@ -77,9 +77,10 @@ class Cache:
         for cid in sorted(requests):
             for req in requests[cid]:
                 if isinstance(req, KVRequest):
-                    sig = (req.kv_heads, req.head_dim, req.window, req.values)
+                    sig = (req.kv_heads, req.head_dim, req.window, req.values, req.keep_first if req.window else 0)
                     gi = next((i for i, g in enumerate(self.kv_groups)
-                               if (g.request.kv_heads, g.request.head_dim, g.request.window, g.request.values) == sig), None)
+                               if (g.request.kv_heads, g.request.head_dim, g.request.window, g.request.values,
+                                   g.request.keep_first if g.request.window else 0) == sig), None)
                     if gi is None:
                         self.kv_groups.append(_KVGroup(req, [], None, None, None, None,
                                                        IndexPool(self.n_pages, "cache page"),
@@ -176,7 +177,8 @@ class Cache:
             if w:
                 first_needed = max(0, L + 1 - w) // PAGE       # the next query at position L sees keys >= L+1-w
                 have = g.pages_of[slot]
-                for i in range(min(first_needed, len(have))):
+                kept = pages_for(max(0, g.request.keep_first))  # pages with positions that every later query still sees
+                for i in range(kept, min(first_needed, len(have))):
                     if have[i] >= 0:
                         g.pool.free(have[i])
                         have[i] = -1

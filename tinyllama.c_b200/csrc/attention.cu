@@ -172,7 +172,8 @@ __global__ void __launch_bounds__(128)
 attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, T* __restrict__ out, int H, int KV,
-                      int hd, float scale, int window, int out_ld, float softcap, int sink) {
+                      int hd, float scale, int window, int out_ld, float softcap, int sink, int keep_first,
+                      const float* __restrict__ sink_values) {
   tlc_pdl(q, k_pages, v_pages, out);
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -192,10 +193,15 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
   float acc[ATT_MAXD];
 #pragma unroll
   for (int i = 0; i < ATT_MAXD; i++) acc[i] = 0.f;
-  for (int k0 = start; k0 < n_keys; k0 += 32) {
+  // with a window, the first keep_first keys of the sequence stay visible: they are walked first (the pieces of 32 keys
+  // before the window's start), then the window; a key between the two is masked
+  const int kept = min(max(keep_first, 0), start);
+  for (int k0 = kept > 0 ? 0 : start; k0 < n_keys; k0 += 32) {
+    if (k0 >= kept && k0 + 32 <= start) { k0 = start - (start % 32) - 32; continue; }   // nothing visible in this piece
     const int kp = k0 + lane;
     float s = -INFINITY;
-    if (kp < n_keys) {
+    const bool seen = kp < n_keys && (kp >= start || kp < kept);
+    if (seen) {
       const int page = table[kp / TLC_PAGE];
       const T* kr = k_pages + (((size_t)page * KV + g) * TLC_PAGE + kp % TLC_PAGE) * hd;
       float dot = 0.f;
@@ -203,7 +209,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
       s = capped_score(dot, softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
-    const float p = kp < n_keys ? expf(s - m_new) : 0.f;
+    const float p = seen ? expf(s - m_new) : 0.f;
     const float corr = expf(m - m_new);      // exp(-inf) = 0 on the first chunk
     l = l * corr + warp_sum(p);
 #pragma unroll
@@ -212,6 +218,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
     for (int j = 0; j < nk; j++) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const int kj = k0 + j;
+      if (kj < start && kj >= kept) continue;          // masked (its page may have been given back)
       const int page = table[kj / TLC_PAGE];
       const T* vr = v_pages + (((size_t)page * KV + g) * TLC_PAGE + kj % TLC_PAGE) * hd;
 #pragma unroll
@@ -222,9 +229,10 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
     }
     m = m_new;
   }
-  if (sink) {                               // one more term of score 0 in the denominator; it carries no value
-    const float m_new = fmaxf(m, 0.f), corr = expf(m - m_new);
-    l = l * corr + expf(-m_new);
+  if (sink) {                               // one more term in the denominator (score 0, or the head's own); it carries no value
+    const float sv = sink_values ? sink_values[h] : 0.f;
+    const float m_new = fmaxf(m, sv), corr = expf(m - m_new);
+    l = l * corr + expf(sv - m_new);
 #pragma unroll
     for (int i = 0; i < ATT_MAXD; i++) acc[i] *= corr;
   }
@@ -240,7 +248,8 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
 extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                              const int* block_table, int max_pages, const int* positions, const int* row_seq,
                              const int* slots, void* out, int T, int H, int KV, int hd, float scale, int window,
-                             int out_ld, float softcap, int sink, cudaStream_t stream) {
+                             int out_ld, float softcap, int sink, int keep_first, const float* sink_values,
+                             cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
@@ -249,7 +258,7 @@ extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, cons
   const size_t smem = (size_t)4 * hd * sizeof(float);
   TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(attention_warp_kernel<TT>, dim3(grid), dim3(128), smem, stream, 
       (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, (TT*)out,
-      H, KV, hd, scale, window, out_ld, softcap, sink));
+      H, KV, hd, scale, window, out_ld, softcap, sink, keep_first, sink_values));
   TLC_CHECK_LAUNCH("attention");
   return 0;
 }
@@ -269,7 +278,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
                                 const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                                 const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
                                 float* __restrict__ part_ml, int H, int KV, int hd, float scale, int window, int n_splits,
-                                float softcap) {
+                                float softcap, int keep_first) {
   tlc_pdl(q, k_pages, v_pages, part_o, part_ml);
   extern __shared__ float sh[];
   const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
@@ -278,8 +287,9 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
   const int n_keys = pos + 1;
   const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
   const int k0 = split * DEC_KEYS;
+  const int kept = min(max(keep_first, 0), start);      // with a window, the sequence's first keys stay visible
   float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;   // + hg * n_splits * 2
-  if (k0 >= n_keys || k0 + DEC_KEYS <= start) {
+  if (k0 >= n_keys || (k0 + DEC_KEYS <= start && k0 >= kept)) {
     if (threadIdx.x < G) { ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY; ml[(size_t)threadIdx.x * n_splits * 2 + 1] = 0.f; }
     return;
   }
@@ -291,7 +301,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
     qs[i] = to_f32(q[((size_t)t * H + (size_t)g * G) * hd + i]) * scale;
   __syncthreads();
   const int kp = k0 + threadIdx.x;
-  const bool valid = kp >= start && kp < n_keys;
+  const bool valid = (kp >= start || kp < kept) && kp < n_keys;
   float s[DEC_MAXG];
 #pragma unroll
   for (int hg = 0; hg < DEC_MAXG; hg++) s[hg] = 0.f;
@@ -325,7 +335,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
     for (int hg = 0; hg < DEC_MAXG; hg++) acc[hg] = 0.f;
     for (int j = 0; j < nk; j++) {
       const int kj = k0 + j;
-      if (kj < start) continue;            // outside the window: its page may have been given back
+      if (kj < start && kj >= kept) continue;   // outside the window: its page may have been given back
       const float vv = to_f32(v_pages[(((size_t)table[kj / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * hd + d]);
 #pragma unroll
       for (int hg = 0; hg < DEC_MAXG; hg++)
@@ -347,7 +357,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
                                     int max_pages, const int* __restrict__ positions, const int* __restrict__ row_seq,
                                     const int* __restrict__ slots, float* __restrict__ part_o,
                                     float* __restrict__ part_ml, int H, int KV, float scale, int window, int n_splits,
-                                    float softcap) {
+                                    float softcap, int keep_first) {
   // Keys of earlier positions were stored by earlier steps; only the row at the query's own
   // position is written by the kernel before this one.  Everything else is fetched before the
   // wait on that kernel (see tlc_pdl).
@@ -361,8 +371,9 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   const int n_keys = pos + 1;
   const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
   const int k0 = split * DEC_KEYS;
+  const int kept = min(max(keep_first, 0), start);      // with a window, the sequence's first keys stay visible
   float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;
-  if (k0 >= n_keys || k0 + DEC_KEYS <= start) {
+  if (k0 >= n_keys || (k0 + DEC_KEYS <= start && k0 >= kept)) {
     tlc_wait(ml);
     if (threadIdx.x < G) { ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY; ml[(size_t)threadIdx.x * n_splits * 2 + 1] = 0.f; }
     return;
@@ -374,7 +385,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   __shared__ int pages[DEC_KEYS / TLC_PAGE + 1];
   const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
   const int kp = k0 + threadIdx.x;
-  const bool valid = kp >= start && kp < n_keys;
+  const bool valid = (kp >= start || kp < kept) && kp < n_keys;
   uint4 kq[DL];
   const uint4* kr = nullptr;
   if (valid) {
@@ -477,7 +488,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
     for (int u = 0; u < VB; u++) {
       const int j = grp + (jb + u) * GROUPS;
       const int kj = k0 + j;
-      const bool use = j < nk && kj >= start;          // outside the window a page may have been given back
+      const bool use = j < nk && (kj >= start || kj < kept);   // outside the window a page may have been given back
       vq[u] = use ? __ldg(reinterpret_cast<const uint4*>(
                               v_pages + (((size_t)pages[j / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl)
                   : make_uint4(0, 0, 0, 0);
@@ -517,14 +528,16 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
 
 template <typename T>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              T* __restrict__ out, int hd, int n_splits, int H, int out_ld, int sink) {
+                                              T* __restrict__ out, int hd, int n_splits, int H, int out_ld, int sink,
+                                              const float* __restrict__ sink_values) {
   tlc_pdl(part_o, part_ml, out);
   const size_t th = blockIdx.x;                       // row * H + head
   T* orow = out + (th / H) * (size_t)out_ld + (th % H) * (size_t)hd;
   const float* ml = part_ml + th * n_splits * 2;
-  float m = sink ? 0.f : -INFINITY;           // (a sink is one more split: maximum 0, sum 1, no values)
+  const float sv = (sink && sink_values) ? sink_values[th % H] : 0.f;
+  float m = sink ? sv : -INFINITY;            // (a sink is one more split: its score the maximum, sum 1, no values)
   for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
-  float l = sink ? expf(-m) : 0.f;
+  float l = sink ? expf(sv - m) : 0.f;
   for (int s = 0; s < n_splits; s++) if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
   const float inv = 1.0f / l;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
@@ -540,7 +553,7 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
                                     const int* block_table, int max_pages, const int* positions, const int* row_seq,
                                     const int* slots, void* out, float* part_o, float* part_ml, int T, int H, int KV,
                                     int hd, float scale, int window, int max_keys, int out_ld, float softcap, int sink,
-                                    cudaStream_t stream) {
+                                    int keep_first, const float* sink_values, cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
@@ -557,12 +570,12 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
     if (vsmem <= 48 * 1024) {
       const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
       if (hd == 64)
-        tlc_launch(attention_decode_partial_vec_kernel<64>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap);
+        tlc_launch(attention_decode_partial_vec_kernel<64>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap, keep_first);
       else if (hd == 128)
-        tlc_launch(attention_decode_partial_vec_kernel<128>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap);
+        tlc_launch(attention_decode_partial_vec_kernel<128>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap, keep_first);
       else
-        tlc_launch(attention_decode_partial_vec_kernel<256>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap);
-      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits, H, out_ld, sink);
+        tlc_launch(attention_decode_partial_vec_kernel<256>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits, softcap, keep_first);
+      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits, H, out_ld, sink, sink_values);
       TLC_CHECK_LAUNCH("attention(decode)");
       return 0;
     }
@@ -570,8 +583,8 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
   TLC_DISPATCH_DTYPE(dtype, TT, {
     tlc_launch(attention_decode_partial_kernel<TT>, dim3(grid), dim3(DEC_KEYS), smem, stream, 
         (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, part_o,
-        part_ml, H, KV, hd, scale, window, n_splits, softcap);
-    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits, H, out_ld, sink);
+        part_ml, H, KV, hd, scale, window, n_splits, softcap, keep_first);
+    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits, H, out_ld, sink, sink_values);
   });
   TLC_CHECK_LAUNCH("attention(decode)");
   return 0;
@@ -615,5 +628,5 @@ extern "C" int tlc_attention_decode_no_alloc(const void* q, int dtype, const voi
   float* part_o = g_decode_scratch_addr[dev];
   float* part_ml = part_o + (size_t)T * H * n_splits * hd;
   return tlc_attention_decode(q, dtype, k_pages, v_pages, block_table, max_pages, positions, row_seq, slots, out, part_o,
-                              part_ml, T, H, KV, hd, scale, window, max_keys, 0, 0.f, 0, stream);
+                              part_ml, T, H, KV, hd, scale, window, max_keys, 0, 0.f, 0, 0, nullptr, stream);
 }

@@ -20,12 +20,24 @@
 
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(float* __restrict__ qkv, int ld, int q_off, int k_off, int G, int dk, float l2_eps, float q_scale,
-                     const float* __restrict__ proj, int ldp, int b_off, int H, float* __restrict__ beta, int T) {
-  tlc_pdl(qkv, proj, beta);
+                     const float* __restrict__ proj, int ldp, int b_off, int H, float* __restrict__ beta, int T,
+                     float* __restrict__ chan, int ldc, const float* __restrict__ A) {
+  tlc_pdl(qkv, proj, beta, chan);
   const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  const int units = 2 * G;
+  const int units = 2 * G + (chan ? H : 0);
   if (w >= T * units) return;
   const int t = w / units, u = w - t * units;
+  if (u >= 2 * G) {       // a decay per key channel of head h, in place: exp(A[h] * softplus(x)), A[h] = -exp(A_log[h])
+    const int h = u - 2 * G;
+    float* c = chan + (size_t)t * ldc + (size_t)h * dk;
+    const float a = A[h];
+    for (int d = lane; d < dk; d += 32) {
+      const float x = c[d];
+      const float sp = x > 20.f ? x : log1pf(expf(x));
+      c[d] = expf(a * sp);
+    }
+    return;
+  }
   if (u == 0)
     for (int h = lane; h < H; h += 32) beta[(size_t)t * H + h] = 1.0f / (1.0f + expf(-proj[(size_t)t * ldp + b_off + h]));
   float* x = qkv + (size_t)t * ld + (u < G ? q_off + u * dk : k_off + (u - G) * dk);
@@ -37,12 +49,14 @@ delta_prepare_kernel(float* __restrict__ qkv, int ld, int q_off, int k_off, int 
 }
 
 extern "C" int tlc_delta_prepare(float* qkv, int ld, int q_off, int k_off, int G, int dk, float l2_eps, float q_scale,
-                                 const float* proj, int ldp, int b_off, int H, float* beta, int T, cudaStream_t stream) {
+                                 const float* proj, int ldp, int b_off, int H, float* beta, int T, float* chan, int ldc,
+                                 const float* A, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(G >= 1 && dk >= 1 && H >= 1, "delta_prepare: bad sizes G=%d dk=%d H=%d", G, dk, H);
-  const long long warps = (long long)T * 2 * G;
+  TLC_REQUIRE(chan == nullptr || (A != nullptr && ldc >= H * dk), "delta_prepare: decays per channel need A [H] and rows of H * dk values");
+  const long long warps = (long long)T * (2 * G + (chan ? H : 0));
   tlc_launch(delta_prepare_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, qkv, ld, q_off, k_off, G, dk, l2_eps, q_scale,
-             proj, ldp, b_off, H, beta, T);
+             proj, ldp, b_off, H, beta, T, chan, ldc, A);
   TLC_CHECK_LAUNCH("delta_prepare");
   return 0;
 }
@@ -66,15 +80,18 @@ template <int N> __device__ __forceinline__ void delta_cp_wait() { asm volatile(
 // strengths arrive in tiles of TT tokens by cp.async, the next tile while the current one is walked.  In shared memory a
 // token's key is laid out thread by thread, DKQ values and DKS - DKQ of padding each, so that the 16-byte pieces the
 // lanes of a quarter warp read lie in different banks.
-template <int DKQ, int NS, int TT>
+// CH: the decay is a vector per token and head, one factor per ROW of S (key channel): decay [T, ldd], head h at column
+// h * dk; it travels with the key, laid out like it.  (a M)^T k is then no multiple of M^T k: the rows are decayed first.
+template <int DKQ, int NS, int TT, bool CH>
 __global__ void __launch_bounds__(DELTA_COLS / DELTA_CT * NS)
 delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* state, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ slots, const int* __restrict__ start_pos, int H, int G, int dk, int dv,
-                  float* __restrict__ y, int ldy, int vec) {
+                  float* __restrict__ y, int ldy, int vec, int ldd) {
   tlc_pdl(qkv, beta, decay, state, y);
   constexpr int CT = DELTA_CT, NT = DELTA_COLS / CT * NS, DKS = DKQ == 4 ? 4 : DKQ + 4, KROW = NS * DKS;
-  constexpr int STAGE = TT * (2 * KROW + DELTA_COLS + 4);           // floats: k, q [TT][KROW]; v [TT][32]; decay, beta [TT][2] (+2)
+  constexpr int NKQ = CH ? 3 : 2;                                   // vectors of dk values a token brings: k, q (and the decays)
+  constexpr int STAGE = TT * (NKQ * KROW + DELTA_COLS + 4);         // floats: k, q (, decays) [TT][KROW]; v [TT][32]; decay, beta [TT][2] (+2)
   __shared__ __align__(16) float sm[2 * STAGE];
   const int b = blockIdx.z, h = blockIdx.y, tid = threadIdx.x;
   const int cg = tid / NS, s = tid % NS;
@@ -106,10 +123,11 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
         const float* row = qkv + (size_t)(ta + tt) * ld;
         delta_cp16(base + at, row + k_off + kvh * dk + r);
         delta_cp16(base + TT * KROW + at, row + q_off + kvh * dk + r);
+        if (CH) delta_cp16(base + 2 * TT * KROW + at, decay + (size_t)(ta + tt) * ldd + h * dk + r);
       }
       for (int i = tid; i < nt * nc4; i += NT) {
         const int tt = i / nc4, cc = (i - tt * nc4) << 2;
-        delta_cp16(base + 2 * TT * KROW + tt * DELTA_COLS + cc, qkv + (size_t)(ta + tt) * ld + v_off + h * dv + j0 + cc);
+        delta_cp16(base + NKQ * TT * KROW + tt * DELTA_COLS + cc, qkv + (size_t)(ta + tt) * ld + v_off + h * dv + j0 + cc);
       }
     } else {
       for (int i = tid; i < nt * dk; i += NT) {
@@ -118,15 +136,16 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
         const float* row = qkv + (size_t)(ta + tt) * ld;
         delta_cp4(base + at, row + k_off + kvh * dk + r);
         delta_cp4(base + TT * KROW + at, row + q_off + kvh * dk + r);
+        if (CH) delta_cp4(base + 2 * TT * KROW + at, decay + (size_t)(ta + tt) * ldd + h * dk + r);
       }
       for (int i = tid; i < nt * n_cols; i += NT) {
         const int tt = i / n_cols, cc = i - tt * n_cols;
-        delta_cp4(base + 2 * TT * KROW + tt * DELTA_COLS + cc, qkv + (size_t)(ta + tt) * ld + v_off + h * dv + j0 + cc);
+        delta_cp4(base + NKQ * TT * KROW + tt * DELTA_COLS + cc, qkv + (size_t)(ta + tt) * ld + v_off + h * dv + j0 + cc);
       }
     }
     if (tid < nt) {
-      delta_cp4(base + 2 * TT * KROW + TT * DELTA_COLS + 2 * tid, decay + (size_t)(ta + tid) * H + h);
-      delta_cp4(base + 2 * TT * KROW + TT * DELTA_COLS + 2 * tid + 1, beta + (size_t)(ta + tid) * H + h);
+      if (!CH) delta_cp4(base + NKQ * TT * KROW + TT * DELTA_COLS + 2 * tid, decay + (size_t)(ta + tid) * H + h);
+      delta_cp4(base + NKQ * TT * KROW + TT * DELTA_COLS + 2 * tid + 1, beta + (size_t)(ta + tid) * H + h);
     }
   };
   if (n_tiles > 0) load(0, 0);
@@ -139,8 +158,9 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
     __syncthreads();
     const float* ks = sm + buf * STAGE + s * DKS;       // this thread's rows of every key
     const float* qs = ks + TT * KROW;
-    const float* vs = sm + buf * STAGE + 2 * TT * KROW + cg * CT;
-    const float* gb = sm + buf * STAGE + 2 * TT * KROW + TT * DELTA_COLS;
+    const float* gs = qs + TT * KROW;                   // (CH) this thread's rows of every token's decays
+    const float* vs = sm + buf * STAGE + NKQ * TT * KROW + cg * CT;
+    const float* gb = sm + buf * STAGE + NKQ * TT * KROW + TT * DELTA_COLS;
     const int ta = t0 + tile * TT, nt = min(TT, t1 - ta);
     for (int tt = 0; tt < nt; tt++) {
       float kk[DKQ], qq[DKQ];
@@ -153,10 +173,21 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
       }
       const float4 vv = *reinterpret_cast<const float4*>(vs + tt * DELTA_COLS);
       const float2 gbt = *reinterpret_cast<const float2*>(gb + 2 * tt);
-      const float g = gbt.x, bt = gbt.y;
+      const float g = CH ? 1.0f : gbt.x, bt = gbt.y;
       float d[CT];
 #pragma unroll
       for (int cc = 0; cc < CT; cc++) d[cc] = 0.f;
+      if (CH) {                                         // every row by its own factor, before the state is asked
+#pragma unroll
+        for (int i = 0; i < DKQ; i += 4) {
+          const float4 gv = *reinterpret_cast<const float4*>(gs + tt * KROW + i);
+          const float gg[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int e = 0; e < 4; e++)
+#pragma unroll
+            for (int cc = 0; cc < CT; cc++) S[i + e][cc] *= gg[e];
+        }
+      }
 #pragma unroll
       for (int i = 0; i < DKQ; i++)
 #pragma unroll
@@ -174,7 +205,7 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
       for (int i = 0; i < DKQ; i++)
 #pragma unroll
         for (int cc = 0; cc < CT; cc++) {
-          S[i][cc] = fmaf(kk[i], u[cc], g * S[i][cc]);
+          S[i][cc] = fmaf(kk[i], u[cc], CH ? S[i][cc] : g * S[i][cc]);
           out[cc] = fmaf(S[i][cc], qq[i], out[cc]);
         }
 #pragma unroll
@@ -209,17 +240,23 @@ extern "C" void tlc_delta_rule_split(int threads) { g_delta_split = (threads == 
 // zero whatever its slot holds); y float [T, ldy] receives the read-outs, head h at column h * dv.  B sequences, T rows in all.
 extern "C" int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, const float* beta, const float* decay,
                               float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int T, int H,
-                              int G, int dk, int dv, float* y, int ldy, cudaStream_t stream) {
+                              int G, int dk, int dv, float* y, int ldy, int ldd, cudaStream_t stream) {
   if (B == 0) return 0;
   TLC_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && H <= 65535 && B <= 65535, "delta_rule: %d heads over %d query/key heads, %d sequences", H, G, B);
   TLC_REQUIRE(dk >= 1 && dk <= 256 && dv >= 1, "delta_rule: keys of %d values exceed the kernel's limit of 256", dk);
   const dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, H, B);
   // whether every piece of four keys, queries or values starts on a 16-byte boundary
   const int vec = ((uintptr_t)qkv % 16 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 && dk % 4 == 0 &&
-                   dv % 4 == 0) ? 1 : 0;
+                   dv % 4 == 0 && (ldd == 0 || ((uintptr_t)decay % 16 == 0 && ldd % 4 == 0))) ? 1 : 0;
+  TLC_REQUIRE(ldd == 0 || ldd >= H * dk, "delta_rule: decays per channel in rows of %d values for %d heads of %d", ldd, H, dk);
+#define DELTA_LAUNCH_AS(DKQ, NS, TT, CH)                                                                                    \
+  tlc_launch(delta_rule_kernel<DKQ, NS, TT, CH>, grid, dim3(DELTA_COLS / DELTA_CT * NS), 0, stream, qkv, ld, q_off, k_off, v_off, beta, \
+             decay, state, cu_seqlens, slots, start_pos, H, G, dk, dv, y, ldy, vec, ldd)
+  // (with a decay per channel a token brings three vectors of dk values: half the tokens a tile where two tiles of
+  // the larger shapes would not fit the 48 KB of static shared memory)
 #define DELTA_LAUNCH(DKQ, NS, TT)                                                                                           \
-  tlc_launch(delta_rule_kernel<DKQ, NS, TT>, grid, dim3(DELTA_COLS / DELTA_CT * NS), 0, stream, qkv, ld, q_off, k_off, v_off, beta, \
-             decay, state, cu_seqlens, slots, start_pos, H, G, dk, dv, y, ldy, vec)
+  do { if (ldd > 0) { DELTA_LAUNCH_AS(DKQ, NS, (TT * (3 * NS * (DKQ == 4 ? 4 : DKQ + 4) + DELTA_COLS + 4) * 8 > 48 * 1024 ? TT / 2 : TT), true); } \
+       else { DELTA_LAUNCH_AS(DKQ, NS, TT, false); } } while (0)
   // threads that share the rows of a column group, unless told otherwise: sixteen with few rows each for prompts, eight
   // with twice the rows for single-token steps (T == B), which move the state once and are bound by that traffic
   // (16 heads of 128 x 128: a 2,048-token prompt 755 against 876 us, 64 single tokens 54 against 34 us)
@@ -229,6 +266,7 @@ extern "C" int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, in
   else if (dk <= 128) { if (ns == 16) DELTA_LAUNCH(8, 16, 8); else DELTA_LAUNCH(16, 8, 16); }
   else DELTA_LAUNCH(16, 16, 8);
 #undef DELTA_LAUNCH
+#undef DELTA_LAUNCH_AS
   TLC_CHECK_LAUNCH("delta_rule");
   return 0;
 }

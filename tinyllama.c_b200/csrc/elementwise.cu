@@ -183,22 +183,28 @@ extern "C" int tlc_rmsnorm(const float* x, int x_ld, const int* rows, const floa
 }
 
 // ---- gate and grouped RMSNorm of the scan output ---------------------------------------
+// the gate of a normed read-out: SiLU of z, or (sig) its sigmoid alone
+__device__ __forceinline__ float gate_f(float z, bool sig) { return sig ? 1.0f / (1.0f + expf(-z)) : silu_f(z); }
+template <bool QUICK> __device__ __forceinline__ float gate_of(float z, bool sig) {
+  return sig ? (QUICK ? __fdividef(1.0f, 1.0f + __expf(-z)) : 1.0f / (1.0f + expf(-z))) : silu_of<QUICK>(z);
+}
 // y [T, Di] 32-bit; z a strided slice of the input projection; out rows of out_ld elements, the whole
 // result times out_scale; one block per (row, group).
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ y2, const TZ* __restrict__ z, int ldz,
-                                     const float* __restrict__ w, float eps, int Di, int gs, int norm_before_gate,
+                                     const float* __restrict__ w, float eps, int Di, int gs, int mode,
                                      TO* __restrict__ out, int out_ld, float out_scale) {
   tlc_pdl(y, y2, z, out);
   __shared__ float red[33];
+  const bool norm_before_gate = mode & TLC_GATE_NORM_FIRST, sig = mode & TLC_GATE_SIGMOID;
   const int t = blockIdx.x, g = blockIdx.y;
   const float* yr = y + (size_t)t * Di + (size_t)g * gs;
   const float* y2r = y2 ? y2 + (size_t)t * Di + (size_t)g * gs : nullptr;    // a second summand of the input
   const TZ* zr = z + (size_t)t * ldz + (size_t)g * gs;
   TO* o = out + (size_t)t * out_ld + (size_t)g * gs;
   if (w == nullptr) {                                   // no norm: y * silu(z)
-    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>((yr[d] + (y2r ? y2r[d] : 0.f)) * silu_f(to_f32(zr[d])) * out_scale);
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>((yr[d] + (y2r ? y2r[d] : 0.f)) * gate_f(to_f32(zr[d]), sig) * out_scale);
     return;
   }
   const float* wg = w + (size_t)g * gs;
@@ -214,7 +220,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ y2, 
     }
 #pragma unroll
     for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
-      gate[i] = silu_f(gate[i]);
+      gate[i] = gate_f(gate[i], sig);
       if (!norm_before_gate) v[i] *= gate[i];
       ss += v[i] * v[i];
     }
@@ -229,13 +235,13 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ y2, 
   }
   for (int d = threadIdx.x; d < gs; d += blockDim.x) {
     float v = yr[d] + (y2r ? y2r[d] : 0.f);
-    if (!norm_before_gate) v *= silu_f(to_f32(zr[d]));
+    if (!norm_before_gate) v *= gate_f(to_f32(zr[d]), sig);
     ss += v * v;
   }
   ss = block_sum(ss, red);
   const float s = out_scale / sqrtf(ss / (float)gs + eps);
   for (int d = threadIdx.x; d < gs; d += blockDim.x) {
-    const float gate = silu_f(to_f32(zr[d]));
+    const float gate = gate_f(to_f32(zr[d]), sig);
     float v = yr[d] + (y2r ? y2r[d] : 0.f);
     v = norm_before_gate ? (v * s * wg[d]) * gate : (v * gate) * s * wg[d];
     o[d] = from_f32<TO>(v);
@@ -247,10 +253,11 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ y2, 
 template <typename TO, int NT, int PT>
 __global__ void __launch_bounds__(NT)
 gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ y2, const float* __restrict__ z, int ldz, const float* __restrict__ w,
-                         float eps, int Di, int gs, int norm_before_gate, TO* __restrict__ out, int out_ld,
+                         float eps, int Di, int gs, int mode, TO* __restrict__ out, int out_ld,
                          float out_scale) {
   asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[33];
+  const bool norm_before_gate = mode & TLC_GATE_NORM_FIRST, sig = mode & TLC_GATE_SIGMOID;
   const int t = blockIdx.x, g = blockIdx.y;
   const int n4 = gs >> 2;
   float4 wv[PT], v[PT], gate[PT];
@@ -277,7 +284,7 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
 #pragma unroll
   for (int i = 0; i < PT; i++) {
     constexpr bool QUICK = sizeof(TO) == 2;              // a bfloat16 output means a bfloat16 run
-    gate[i] = make_float4(silu_of<QUICK>(gate[i].x), silu_of<QUICK>(gate[i].y), silu_of<QUICK>(gate[i].z), silu_of<QUICK>(gate[i].w));
+    gate[i] = make_float4(gate_of<QUICK>(gate[i].x, sig), gate_of<QUICK>(gate[i].y, sig), gate_of<QUICK>(gate[i].z, sig), gate_of<QUICK>(gate[i].w, sig));
     if (!norm_before_gate) { v[i].x *= gate[i].x; v[i].y *= gate[i].y; v[i].z *= gate[i].z; v[i].w *= gate[i].w; }
     ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
   }
@@ -303,8 +310,9 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_warp_kernel(const float* __restrict__ y, const float* __restrict__ y2, const float* __restrict__ z, int ldz,
                           const float* __restrict__ w, float eps, long long n_rows, int n_groups, int Di, int gs,
-                          int norm_before_gate, TO* __restrict__ out, int out_ld, float out_scale) {
+                          int mode, TO* __restrict__ out, int out_ld, float out_scale) {
   asm volatile("griddepcontrol.launch_dependents;");
+  const bool norm_before_gate = mode & TLC_GATE_NORM_FIRST, sig = mode & TLC_GATE_SIGMOID;
   const long long idx = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31, n4 = gs >> 2;
   const bool on = idx < n_rows && lane < n4;
@@ -323,7 +331,7 @@ gated_rmsnorm_warp_kernel(const float* __restrict__ y, const float* __restrict__
     }
   }
   constexpr bool QUICK = sizeof(TO) == 2;                // a bfloat16 output means a bfloat16 run
-  gate = make_float4(silu_of<QUICK>(gate.x), silu_of<QUICK>(gate.y), silu_of<QUICK>(gate.z), silu_of<QUICK>(gate.w));
+  gate = make_float4(gate_of<QUICK>(gate.x, sig), gate_of<QUICK>(gate.y, sig), gate_of<QUICK>(gate.z, sig), gate_of<QUICK>(gate.w, sig));
   if (!norm_before_gate) { v.x *= gate.x; v.y *= gate.y; v.z *= gate.z; v.w *= gate.w; }
   const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
   const float s = out_scale / sqrtf(ss / (float)gs + eps);
@@ -336,7 +344,7 @@ gated_rmsnorm_warp_kernel(const float* __restrict__ y, const float* __restrict__
 }
 
 extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
-                                 int Di, int n_groups, int norm_before_gate, void* out, int out_dtype, int out_ld,
+                                 int Di, int n_groups, int mode, void* out, int out_dtype, int out_ld,
                                  float out_scale, cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = Di;                          // elements between rows of out (0: dense)
@@ -350,21 +358,21 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z,
     if (n4 <= 32) {
       const long long n_rows = (long long)T * n_groups;
       TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_warp_kernel<TO>, dim3((unsigned)((n_rows + 7) / 8)), dim3(256), 0, stream,
-                                                   y, y2, (const float*)z, ldz, w, eps, n_rows, n_groups, Di, gs, norm_before_gate,
+                                                   y, y2, (const float*)z, ldz, w, eps, n_rows, n_groups, Di, gs, mode,
                                                    (TO*)out, out_ld, out_scale));
       TLC_CHECK_LAUNCH("gated_rmsnorm");
       return 0;
     }
 #define TLC_GRMS_LAUNCH(NT, PT)                                                                                         \
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y, y2,    \
-                                               (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale))
+                                               (const float*)z, ldz, w, eps, Di, gs, mode, (TO*)out, out_ld, out_scale))
     if (T >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_GRMS_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_GRMS_LAUNCH) }
 #undef TLC_GRMS_LAUNCH
     TLC_CHECK_LAUNCH("gated_rmsnorm");
     return 0;
   }
   TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_kernel<TZ, TO>, dim3(grid), dim3(256), 0, stream, 
-      y, y2, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale)));
+      y, y2, (const TZ*)z, ldz, w, eps, Di, gs, mode, (TO*)out, out_ld, out_scale)));
   TLC_CHECK_LAUNCH("gated_rmsnorm");
   return 0;
 }
@@ -635,7 +643,8 @@ extern "C" int tlc_gather_rows(const float* x, const int* rows, int R, int D, fl
 
 // ---- a copy of 32-bit rows in the activation type, optionally through tanh ---------------------------------
 // Layers whose sublayers read the residual stream itself (no norm in front) take it from here in the type their
-// products want; act 1: tanh of every element first (the hidden layer of a small two-layer projection).
+// products want; act 1: tanh of every element first (the hidden layer of a small two-layer projection); act 2: the square
+// of max(x, 0) (the activation of a feed-forward without a gate).
 template <typename TO>
 __global__ void convert_kernel(const float* __restrict__ x, int ldx, int D, TO* __restrict__ out, int ldo, size_t total, int act) {
   tlc_pdl(x, out);
@@ -644,12 +653,13 @@ __global__ void convert_kernel(const float* __restrict__ x, int ldx, int D, TO* 
   const size_t t = i / D;
   const int d = (int)(i % D);
   const float v = x[t * ldx + d];
-  out[t * ldo + d] = from_f32<TO>(act == 1 ? tanhf(v) : v);
+  const float r = fmaxf(v, 0.f);
+  out[t * ldo + d] = from_f32<TO>(act == 1 ? tanhf(v) : act == 2 ? r * r : v);
 }
 extern "C" int tlc_convert(const float* x, int ldx, int T, int D, void* out, int dtype, int ldo, int act, cudaStream_t stream) {
   const size_t total = (size_t)T * D;
   if (total == 0) return 0;
-  TLC_REQUIRE(act == 0 || act == 1, "convert: unknown function %d (0 none, 1 tanh)", act);
+  TLC_REQUIRE(act >= 0 && act <= 2, "convert: unknown function %d (0 none, 1 tanh, 2 squared relu)", act);
   TLC_DISPATCH_DTYPE(dtype, TO, tlc_launch(convert_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, ldx, D,
                                            (TO*)out, ldo, total, act));
   TLC_CHECK_LAUNCH("convert");

@@ -22,7 +22,7 @@
 // warp the best of the lanes.
 __global__ void __launch_bounds__(128)
 moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int mode, const float* __restrict__ choice_bias,
-                int* __restrict__ ids, float* __restrict__ wts) {
+                int* __restrict__ ids, float* __restrict__ wts, float sum_to) {
   tlc_pdl(logits, ids, wts);
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -69,7 +69,9 @@ moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
         sum += e;
         wts[t * top + k] = e;
       } else if (mode == TLC_ROUTE_SOFTMAX_ALL) {
-        wts[t * top + k] = __fmul_rn(expf(lr[be] - all_max), all_inv);
+        const float w = __fmul_rn(expf(lr[be] - all_max), all_inv);
+        sum += w;
+        wts[t * top + k] = w;
       } else {
         wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
       }
@@ -80,6 +82,11 @@ moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
   if (mode == TLC_ROUTE_SOFTMAX && lane == 0) {
     const float inv = 1.0f / sum;
     for (int k = 0; k < top; k++) wts[t * top + k] *= inv;
+  }
+  // the chosen scores divided by their sum (+ 1e-20, which keeps a sum of zero finite) and multiplied by sum_to
+  if (mode == TLC_ROUTE_SOFTMAX_ALL && sum_to > 0.f && lane == 0) {
+    const float inv = 1.0f / (sum + 1e-20f);
+    for (int k = 0; k < top; k++) wts[t * top + k] = wts[t * top + k] * inv * sum_to;
   }
 }
 
@@ -113,13 +120,14 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int E_tiled, in
 }
 
 extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, const float* choice_bias, int n_identity,
-                             int* ids, float* wts, int* order, int* offsets, int* tile_off, int tile_rows, cudaStream_t stream) {
+                             int* ids, float* wts, int* order, int* offsets, int* tile_off, int tile_rows, float sum_to,
+                             cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(tile_rows >= 1, "moe_route: tiles of %d rows", tile_rows);
   TLC_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096, "moe_route: %d experts, %d chosen", E, top);
   TLC_REQUIRE(mode == TLC_ROUTE_SIGMOID || mode == TLC_ROUTE_SOFTMAX || mode == TLC_ROUTE_SOFTMAX_ALL, "moe_route: unknown weighting %d", mode);
   TLC_REQUIRE(n_identity >= 0 && n_identity < E, "moe_route: %d of %d router outputs without an expert's weights", n_identity, E);
-  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, mode, choice_bias, ids, wts);
+  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, mode, choice_bias, ids, wts, sum_to);
   TLC_CHECK_LAUNCH("moe_topk");
   tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, E - n_identity, tile_rows,
              order, offsets, tile_off);

@@ -4,7 +4,9 @@
 // tlc_qk_rotate_norm works on the 32-bit projection in place, a warp per (row, head), query heads and key heads alike:
 // it turns the pairs of the first `rot` dimensions of a head by angle = position * inv_freq[i] (pairs (2i, 2i+1) with
 // interleaved != 0, else (i, i + rot/2); dimensions past `rot` pass unchanged) and then, with norm_eps >= 0, scales the
-// head to unit root mean square over its `dim` dimensions, x / sqrt(mean(x^2) + eps), without a weight.  Heads may lie
+// head to unit root mean square over its `dim` dimensions, x / sqrt(mean(x^2) + eps), without a weight.  With q_w and k_w
+// (weights [dim], one for all query heads and one for all key heads) every head is first normed BEFORE the rotation,
+// x / sqrt(mean(x^2) + pre_eps) * w; `amplitude` multiplies every cosine and sine (1: a plain rotation).  Heads may lie
 // `stride` >= dim values apart (a mixer whose values are wider than its keys pads the heads; the padding stays zero).
 // Everything is 32-bit; the kernels that store keys and values then need not rotate.
 //
@@ -17,7 +19,8 @@
 __global__ void __launch_bounds__(128)
 qk_rotate_norm_kernel(float* __restrict__ qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim,
                       const float* __restrict__ inv_freq, int rot, int interleaved, float norm_eps,
-                      const int* __restrict__ positions, int T) {
+                      const int* __restrict__ positions, int T, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                      float pre_eps, float amplitude) {
   tlc_pdl(qkv);
   const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int units = H + KV;
@@ -26,17 +29,30 @@ qk_rotate_norm_kernel(float* __restrict__ qkv, int ld, int q_off, int k_off, int
   float* x = qkv + (size_t)t * ld + (u < H ? q_off + u * stride : k_off + (u - H) * stride);
   const float fpos = (float)positions[t];
   const int half = rot >> 1;
+  // a weighted RMS norm of the head BEFORE the rotation (pre_w): x <- x / sqrt(mean(x^2) + pre_eps) * pre_w
+  const float* pre_w = u < H ? q_w : k_w;
+  float pre = 1.0f;
+  if (pre_w) {
+    float p2 = 0.f;
+    for (int d = lane; d < dim; d += 32) { const float v = x[d]; p2 += v * v; }
+    pre = 1.0f / sqrtf(warp_sum(p2) / (float)dim + pre_eps);
+  }
   float ss = 0.f;
   for (int p = lane; p < half; p += 32) {
     const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
     float sn, cs;
     sincosf(fpos * inv_freq[p], &sn, &cs);
-    const float a = x[ia], b = x[ib];
+    sn *= amplitude;
+    cs *= amplitude;
+    float a = x[ia], b = x[ib];
+    if (pre_w) { a = a * pre * pre_w[ia]; b = b * pre * pre_w[ib]; }
     const float ra = a * cs - b * sn, rb = b * cs + a * sn;
     x[ia] = ra;
     x[ib] = rb;
     ss += ra * ra + rb * rb;
   }
+  if (pre_w)
+    for (int d = rot + lane; d < dim; d += 32) x[d] = x[d] * pre * pre_w[d];
   if (norm_eps < 0.f) return;
   for (int d = rot + lane; d < dim; d += 32) { const float v = x[d]; ss += v * v; }
   ss = warp_sum(ss);
@@ -47,13 +63,14 @@ qk_rotate_norm_kernel(float* __restrict__ qkv, int ld, int q_off, int k_off, int
 
 extern "C" int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim,
                                   const float* inv_freq, int rot, int interleaved, float norm_eps, const int* positions, int T,
-                                  cudaStream_t stream) {
+                                  const float* q_w, const float* k_w, float pre_eps, float amplitude, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(dim >= 1 && dim <= stride && rot >= 0 && rot % 2 == 0 && rot <= dim, "qk_rotate_norm: %d rotated of %d dimensions, heads %d apart",
               rot, dim, stride);
+  TLC_REQUIRE((q_w == nullptr) == (k_w == nullptr), "qk_rotate_norm: the weights of the norm before the rotation come together");
   const long long warps = (long long)T * (H + KV);
   tlc_launch(qk_rotate_norm_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, qkv, ld, q_off, k_off, H, KV, stride, dim,
-             inv_freq, rot, interleaved, norm_eps, positions, T);
+             inv_freq, rot, interleaved, norm_eps, positions, T, q_w, k_w, pre_eps, amplitude);
   TLC_CHECK_LAUNCH("qk_rotate_norm");
   return 0;
 }

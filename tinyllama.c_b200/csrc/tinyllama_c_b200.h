@@ -74,10 +74,25 @@ int tlc_embed(const int* tokens, const void* table, int table_dtype, int T, int 
  * columns of a wider matrix will do); out [R, D] of out_dtype. */
 int tlc_rmsnorm(const float* x, int x_ld, const int* rows, const float* w, float eps, int R, int D, void* out,
                 int out_dtype, cudaStream_t stream);
+/* Layer norm without a bias: out1[r] = (x - mean) / sqrt(var + eps) * w1 with var the mean of the squared deviations, x as in
+ * tlc_rmsnorm.  w2 and out2 (both or neither): the same normed row times a second weight, for a layer whose two sublayers each
+ * norm the same rows. */
+int tlc_layernorm(const float* x, int x_ld, const int* rows, const float* w1, const float* w2, float eps, int R, int D,
+                  void* out1, void* out2, int out_dtype, cudaStream_t stream);
+/* x[t, :D] += v[:D] for every row of x float [T, D]. */
+int tlc_add_row(float* x, const float* v, int T, int D, cudaStream_t stream);
+/* Two attention maps per query head over the same values: out[t, h] = o / sqrt(mean(o^2) + eps) * out_scale with
+ * o = a1 - lambda a2 over vd values.  att [T, ld_in] holds virtual heads of hd values: the first map of head h (group
+ * g = h / per_group) at virtual head 2 g per_group + (h - g per_group), the second per_group heads further on; out
+ * [T, ld_out], head h at column h * hd_out. */
+int tlc_difference_join(const void* att, int dtype, int ld_in, int hd, void* out, int ld_out, int hd_out, int T, int H,
+                        int per_group, int vd, float lambda, float eps, float out_scale, cudaStream_t stream);
 /* Gate y (+ y2, where y2 is not NULL: an input that comes as two summands) by silu(z) and RMS-normalise per group,
  * in either order; w NULL: gate only.  out [T, Di] with row stride out_ld, multiplied by out_scale. */
+#define TLC_GATE_NORM_FIRST 1   /* mode bit: the norm comes before the gate */
+#define TLC_GATE_SIGMOID 2      /* mode bit: the gate is sigmoid(z), not silu(z) */
 int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
-                      int Di, int n_groups, int norm_before_gate, void* out, int out_dtype, int out_ld,
+                      int Di, int n_groups, int mode, void* out, int out_dtype, int out_ld,
                       float out_scale, cudaStream_t stream);
 /* out[T, F] = silu(gate) * up; gu holds gate | up as halves, or (interleave) 8 gates then their 8 ups. */
 int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave,
@@ -87,7 +102,7 @@ int tlc_gather_rows(const float* x, const int* rows, int R, int D, float* out, c
  * g = min(gate, limit) and u = up held within +-limit, g * sigmoid(alpha g) * (u + 1). */
 int tlc_glu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave, int act,
             float limit, float alpha, cudaStream_t stream);
-/* out[t, :D] = x[t, :D] (act 0) or tanh(x[t, :D]) (act 1) in the given type; row strides ldx, ldo. */
+/* out[t, :D] = x[t, :D] (act 0), tanh(x[t, :D]) (act 1) or max(x[t, :D], 0)^2 (act 2) in the given type; row strides ldx, ldo. */
 int tlc_convert(const float* x, int ldx, int T, int D, void* out, int dtype, int ldo, int act, cudaStream_t stream);
 /* x[i] = cap * tanh(x[i] / cap) for n values, in place. */
 int tlc_softcap(float* x, long long n, float cap, cudaStream_t stream);
@@ -164,18 +179,20 @@ int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int ld, int q_of
                       int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream);
 /* Causal grouped-query attention of every row over its sequence's pages (keys 0..position, or the last
  * `window`); any sizes, both element types; a warp per (row, head).  softcap > 0: score <- softcap * tanh(score /
- * softcap) after the scale; sink: one more term of score 0 in the softmax's denominator, which carries no value. */
+ * softcap) after the scale; sink: one more term of score 0 in the softmax's denominator, which carries no value
+ * (sink_values not NULL: of score sink_values[head], not scaled).  keep_first > 0 with a window: the first keep_first keys
+ * of the sequence stay visible to every query at their own positions. */
 int tlc_attention(const void* q, int dtype, const void* k_pages, const void* v_pages, const int* block_table,
                   int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
-                  int H, int KV, int hd, float scale, int window, int out_ld, float softcap, int sink,
-                  cudaStream_t stream);
+                  int H, int KV, int hd, float scale, int window, int out_ld, float softcap, int sink, int keep_first,
+                  const float* sink_values, cudaStream_t stream);
 /* Single-token rows: keys split across blocks of 128, partial results in part_o [T, H, splits, hd] and
  * part_ml [T, H, splits, 2], then merged. */
 int tlc_attention_decode(const void* q, int dtype, const void* k_pages, const void* v_pages,
                          const int* block_table, int max_pages, const int* positions, const int* row_seq,
                          const int* slots, void* out, float* part_o, float* part_ml, int T, int H, int KV,
                          int hd, float scale, int window, int max_keys, int out_ld, float softcap, int sink,
-                         cudaStream_t stream);
+                         int keep_first, const float* sink_values, cudaStream_t stream);
 /* Single-token rows of a bfloat16 cache in one kernel: rotation of q and the new key, store of the new
  * K/V row, scores and outputs on the tensor cores, merge of the splits by the last block to arrive
  * (arrivals: zeroed counters, at least T*KV, back at zero afterwards). */
@@ -298,11 +315,14 @@ int tlc_mingru_scan(const float* proj, int ld, int z_off, int u_off, int g_off, 
  * tlc_qk_rotate_norm, in place on the float projection qkv [T, ld] (H query heads from q_off, KV key heads from k_off,
  * heads `stride` values apart, `dim` <= stride of them in use): the pairs of the first `rot` dimensions turn by
  * position * inv_freq[i] (pairs (2i, 2i+1) with interleaved != 0, else (i, i + rot/2)); then, with norm_eps >= 0, the
- * head is divided by sqrt(mean over dim of x^2 + norm_eps).
+ * head is divided by sqrt(mean over dim of x^2 + norm_eps).  q_w, k_w (float [dim], both or neither): before the rotation
+ * every query head becomes x / sqrt(mean(x^2) + pre_eps) * q_w, every key head likewise with k_w.  amplitude multiplies the
+ * cosines and sines.
  * tlc_gate_mul: x[t, c] *= sigmoid(gate[t, c]) (act 0) or silu(gate[t, c]) (act 1); x [T, n] of `dtype`, row stride ldx;
  * gate float, row stride ldg. */
 int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim, const float* inv_freq,
-                       int rot, int interleaved, float norm_eps, const int* positions, int T, cudaStream_t stream);
+                       int rot, int interleaved, float norm_eps, const int* positions, int T, const float* q_w,
+                       const float* k_w, float pre_eps, float amplitude, cudaStream_t stream);
 int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n, int T, int act, cudaStream_t stream);
 /* In place on the 32-bit projection: the q_n query columns from q_off, all heads together, are divided by their root mean
  * square (eps inside the root) and multiplied by qw [q_n]; the k_n key columns from k_off likewise with kw [k_n]. */
@@ -315,13 +335,16 @@ int tlc_qk_whole_norm(float* qkv, int ld, int q_off, int q_n, const float* qw, i
  * [n_slots, H, dk, dv] (zero at position 0).  tlc_delta_prepare normalises, in place in qkv [T, ld] float, the G query
  * heads at q_off (x / sqrt(sum x^2 + l2_eps) * q_scale) and the G key heads at k_off (the same without the scale), and
  * writes beta[t, h] = sigmoid(proj[t, b_off + h]).  tlc_delta_rule walks every sequence's rows: values (H heads of dv) at
- * v_off, beta and decay float [T, H]; y [T, ldy] float receives the read-outs (head h at column h * dv). */
+ * v_off, beta and decay float [T, H]; y [T, ldy] float receives the read-outs (head h at column h * dv).
+ * A decay per key channel: tlc_delta_prepare with chan [T, ldc] (head h's dk values at column h * dk) and A [H] turns chan,
+ * in place, into exp(A[h] * softplus(chan)); tlc_delta_rule with ldd > 0 takes decay [T, ldd] laid out like that and
+ * multiplies row r of M by its own factor: M <- diag(a) M. */
 int tlc_delta_prepare(float* qkv, int ld, int q_off, int k_off, int G, int dk, float l2_eps, float q_scale, const float* proj,
-                      int ldp, int b_off, int H, float* beta, int T, cudaStream_t stream);
+                      int ldp, int b_off, int H, float* beta, int T, float* chan, int ldc, const float* A, cudaStream_t stream);
 void tlc_delta_rule_split(int threads);   /* threads that share the rows of a column group: 8 or 16 (0: chosen); for tests */
 int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, const float* beta, const float* decay,
                    float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int T, int H, int G,
-                   int dk, int dv, float* y, int ldy, cudaStream_t stream);
+                   int dk, int dv, float* y, int ldy, int ldd, cudaStream_t stream);
 
 /* ---- mixture of experts (moe.cu) ------------------------------------------------------------------------
  * tlc_moe_route: logits float [T, ld] (E columns) -> per token its `top` experts by descending logit (lowest index
@@ -332,9 +355,10 @@ int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, co
 /* TLC_ROUTE_SOFTMAX_ALL: scores s = softmax over all E outputs; chosen by s + choice_bias[e] (choice_bias NULL: by s),
  * weighted by s.  The last n_identity of the E outputs have no expert's weights (they stand for experts that return their
  * input, tlc_moe_identity): their pairs are sorted behind the others and get no tiles, and the expert products are called
- * with E - n_identity experts. */
+ * with E - n_identity experts.  sum_to > 0 (TLC_ROUTE_SOFTMAX_ALL): a token's weights are divided by their sum (+ 1e-20) and
+ * multiplied by sum_to. */
 int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, const float* choice_bias, int n_identity,
-                  int* ids, float* wts, int* order, int* offsets, int* tile_off, int tile_rows, cudaStream_t stream);
+                  int* ids, float* wts, int* order, int* offsets, int* tile_off, int tile_rows, float sum_to, cudaStream_t stream);
 /* y[pair, :D] = wts[pair] * x[token(pair), :D] for every pair with ids[pair] >= E. */
 int tlc_moe_identity(const void* x, int x_dtype, int ldx, const int* ids, const float* wts, int T, int top, int E, int D,
                      float* y, cudaStream_t stream);

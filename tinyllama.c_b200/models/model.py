@@ -22,7 +22,10 @@ from ..parts.linear import StackedLinear, matrix_dtype
 class Model:
     def __init__(self, config, layer_specs: Sequence[LayerSpec], schedule: Optional[Sequence[LayerRun]],
                  final_norm: PartSpec, embed_name: str, head_name: Optional[str], vocab: int, hidden: int,
-                 embed_scale: float = 1.0, head_scale: float = 1.0, logit_softcap: float = 0.0):
+                 embed_scale: float = 1.0, head_scale: float = 1.0, logit_softcap: float = 0.0,
+                 row_tables: Optional[Dict[str, int]] = None):
+        """row_tables: learned tables [rows, hidden] by tensor name -> number of rows; an entry of the run order may name a
+        row that is added to the residual stream before it runs (LayerRun.add)."""
         self.config = config
         self.vocab, self.hidden = int(vocab), int(hidden)
         self.layers: List[Block] = [Block(s) for s in layer_specs]
@@ -36,6 +39,8 @@ class Model:
             if run.cache is not None and any(isinstance(q, StateRequest) for q in self.layers[run.layer].cache_requests()):
                 raise ValueError(f"run-order entry {r} reads the cache of entry {run.cache} but layer {run.layer} has a "
                                  f"mixer with state of its own: only keys and values can be read without storing")
+            if run.add is not None and not (row_tables and run.add[0] in row_tables and 0 <= run.add[1] < row_tables[run.add[0]]):
+                raise ValueError(f"run-order entry {r} adds row {run.add!r}, which no table of the model has")
             if run.kv_cache is not None:
                 # keys and values of an EARLIER entry with a cache of its own: its rows of this step are stored
                 # before this entry reads them
@@ -59,6 +64,8 @@ class Model:
         self.logit_softcap = float(logit_softcap)          # > 0: logits <- cap * tanh(logits / cap)
         self.head = StackedLinear(hidden)
         self.head.add(head_name or embed_name, vocab, None, 1.0, head_scale)
+        self.row_tables = {k: int(v) for k, v in (row_tables or {}).items()}
+        self.rows_of: Dict[str, torch.Tensor] = {}
         self.embed_table: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
@@ -71,6 +78,7 @@ class Model:
         for layer in self.layers:
             specs += layer.weight_specs()
         specs += self.final_norm.weight_specs()
+        specs += [WeightSpec(name, (rows, self.hidden), "normal") for name, rows in self.row_tables.items()]
         seen, out = set(), []
         for s in specs:
             if s.name not in seen:
@@ -102,6 +110,7 @@ class Model:
         for layer in self.layers:
             layer.bind(tensors, dtype, device)
         self.final_norm.bind(tensors, dtype, device)
+        self.rows_of = {name: tensors[name].to(device=device, dtype=torch.float32).contiguous() for name in self.row_tables}
         emb = tensors[self.embed_name]
         self.embed_table = emb.to(device=device, dtype=matrix_dtype(emb.dtype, dtype)).contiguous()
         if self.head_name is None:
@@ -122,7 +131,11 @@ class Model:
         with step_scratch(step):                       # the layers share the step's temporaries
             ready = False                              # whether a layer left the stream in the activation type for the next
             for r, run in enumerate(self.schedule):
-                wanted = r + 1 < len(self.schedule) and self.layers[self.schedule[r + 1].layer].reads_stream_copy
+                if run.add is not None:            # a learned row joins the stream before this entry (a pass of a repeated range)
+                    ops.add_row(x, self.rows_of[run.add[0]][run.add[1]])
+                    ready = False
+                wanted = r + 1 < len(self.schedule) and self.layers[self.schedule[r + 1].layer].reads_stream_copy \
+                    and self.schedule[r + 1].add is None
                 ready = self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes,
                                                                                  run.kv_cache), ready, wanted)
         if want_rows is None or want_rows.numel() == 0:

@@ -42,6 +42,9 @@ _SIGNATURES = {
     "tlc_selftest_bounded_wait": (_i, [_vp]),
     "tlc_embed": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
     "tlc_rmsnorm": (_i, [_vp, _i, _vp, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_layernorm": (_i, [_vp, _i, _vp, _vp, _vp, _f, _i, _i, _vp, _vp, _i, _vp]),
+    "tlc_add_row": (_i, [_vp, _vp, _i, _i, _vp]),
+    "tlc_difference_join": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp]),
     "tlc_gated_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp]),
     "tlc_swiglu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "tlc_gather_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
@@ -65,9 +68,9 @@ _SIGNATURES = {
     "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                _i, _i, _vp]),
-    "tlc_attention": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _f, _i, _vp]),
+    "tlc_attention": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _f, _i, _i, _vp, _vp]),
     "tlc_attention_decode": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
-                                  _i, _f, _i, _vp]),
+                                  _i, _f, _i, _i, _vp, _vp]),
     "tlc_attention_decode_fused_ok": (_i, [_i, _i, _i]),
     "tlc_attention_decode_fused_passes": (_i, [_i]),
     "tlc_attention_decode_fused": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp,
@@ -114,13 +117,13 @@ _SIGNATURES = {
     "tlc_linear_heads_mma": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _f, _f, _vp]),
     "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
-    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _f, _vp]),
     "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),
-    "tlc_qk_rotate_norm": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _f, _vp, _i, _vp]),
+    "tlc_qk_rotate_norm": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _f, _vp, _i, _vp, _vp, _f, _f, _vp]),
     "tlc_gate_mul": (_i, [_vp, _i, _i, _vp, _i, _i, _i, _i, _vp]),
-    "tlc_delta_prepare": (_i, [_vp, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_delta_prepare": (_i, [_vp, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp]),
     "tlc_delta_rule_split": (None, [_i]),
-    "tlc_delta_rule": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_delta_rule": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "tlc_moe_down": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
@@ -278,8 +281,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tensor], eps: float, n_groups: int,
                   norm_before_gate: bool, out: torch.Tensor, out_scale: float = 1.0,
-                  y_add: Optional[torch.Tensor] = None) -> None:
-    """Gate y by silu(z) and RMS-normalise per group (either order); weight None = gate only.  The
+                  y_add: Optional[torch.Tensor] = None, gate: str = "silu") -> None:
+    """Gate y by silu(z) (or, gate "sigmoid", by sigmoid(z)) and RMS-normalise per group (either order); weight None = gate only.  The
     result is multiplied by out_scale; out [T, Di] may be a range of the columns of a wider buffer.
     y_add: a second summand of the input (the scan of prompts leaves its outputs as two), same shape as y."""
     _gpu(y, z, weight, out, y_add)
@@ -293,8 +296,8 @@ def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tenso
         raise KernelError("gated_rmsnorm: gate and input differ in shape")
     _f32vec(weight, Di, "gated_rmsnorm weight")
     _call("tlc_gated_rmsnorm", y.data_ptr(), _p(y_add), z.data_ptr(), dtype_code(z.dtype), _rows(z, "gate"), _p(weight),
-          float(eps), T, Di, int(n_groups), int(bool(norm_before_gate)), out.data_ptr(), dtype_code(out.dtype),
-          out_ld, float(out_scale), _stream())
+          float(eps), T, Di, int(n_groups), int(bool(norm_before_gate)) | (2 if gate == "sigmoid" else 0), out.data_ptr(),
+          dtype_code(out.dtype), out_ld, float(out_scale), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
@@ -332,15 +335,66 @@ def glu(gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu", interleaved
           out.data_ptr(), dtype_code(out.dtype), int(bool(interleaved)), DENSE_ACTS[act], float(limit), float(alpha), _stream())
 
 
+CONVERT_ACTS = {"none": 0, "tanh": 1, "relu_squared": 2}
+
+
 def convert(x: torch.Tensor, out: torch.Tensor, act: str = "none") -> None:
-    """out = x (float32 [T, D], dense rows) in out's type, or with act "tanh" its tanh; out may be a range of the columns
-    of a wider buffer."""
+    """out = x (float32 [T, D], dense rows) in out's type, or with act "tanh" its tanh, with "relu_squared" max(x, 0)^2; out
+    may be a range of the columns of a wider buffer."""
     _gpu(x, out)
     T, D = x.shape
-    if x.dtype != torch.float32 or act not in ("none", "tanh"):
-        raise KernelError("convert: a float32 input; act 'none' or 'tanh'")
+    if x.dtype != torch.float32 or act not in CONVERT_ACTS:
+        raise KernelError(f"convert: a float32 input; act one of {sorted(CONVERT_ACTS)}")
     _call("tlc_convert", x.data_ptr(), _rows(x, "convert input"), T, D, out.data_ptr(), dtype_code(out.dtype),
-          _out_rows(out, T, D, "convert"), int(act == "tanh"), _stream())
+          _out_rows(out, T, D, "convert"), CONVERT_ACTS[act], _stream())
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+              weight2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (x - mean(x)) / sqrt(var(x) + eps) * weight for x[rows[r]] or x[r] (float32 [*, D], dense rows), var the
+    mean of the squared deviations; no bias.  weight2 and out2 (both or neither): the same normed rows times a second
+    weight (two sublayers that each norm the same rows)."""
+    _gpu(x, weight, out, rows, weight2, out2)
+    D = x.shape[1]
+    R = out.shape[0]
+    if x.dtype != torch.float32 or not out.is_contiguous() or out.shape[1] != D:
+        raise KernelError("layernorm: x must be float32 and out contiguous [R, D]")
+    if (weight2 is None) != (out2 is None) or (out2 is not None and (not out2.is_contiguous() or out2.shape != out.shape
+                                                                     or out2.dtype != out.dtype)):
+        raise KernelError("layernorm: a second weight comes with a second output of the first one's shape and type")
+    _f32vec(weight, D, "layernorm weight")
+    _f32vec(weight2, D, "layernorm second weight")
+    if rows is not None:
+        _i32(rows, "layernorm rows")
+        if rows.numel() != R:
+            raise KernelError("layernorm: one row index per output row")
+    elif x.shape[0] != R:
+        raise KernelError("layernorm: x and out differ in rows")
+    _call("tlc_layernorm", x.data_ptr(), _rows(x, "layernorm input"), _p(rows), weight.data_ptr(), _p(weight2), float(eps), R, D,
+          out.data_ptr(), _p(out2), dtype_code(out.dtype), _stream())
+
+
+def add_row(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[t] += v for every row of x (contiguous float32 [T, D]); v float32 [D]."""
+    _gpu(x, v)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
+        raise KernelError("add_row: x must be contiguous float32 [T, D]")
+    _f32vec(v, x.shape[1], "add_row vector")
+    _call("tlc_add_row", x.data_ptr(), v.data_ptr(), x.shape[0], x.shape[1], _stream())
+
+
+def difference_join(att: torch.Tensor, hd: int, out: torch.Tensor, hd_out: int, H: int, per_group: int, vd: int, lam: float,
+                    eps: float, out_scale: float) -> None:
+    """Two attention maps a query head: att [T, 2 * H * hd] holds virtual heads of hd values, the first map of head h (group
+    g = h // per_group) at virtual head 2 g per_group + (h - g per_group), the second per_group heads further on;
+    out[t, h * hd_out : + vd] = o / sqrt(mean(o^2) + eps) * out_scale with o = a1 - lam * a2 over the first vd values."""
+    _gpu(att, out)
+    T = att.shape[0]
+    if att.dtype != out.dtype or att.shape[1] != 2 * H * hd:
+        raise KernelError("difference_join: maps and result of one type, 2 * H heads of hd values in")
+    _call("tlc_difference_join", att.data_ptr(), dtype_code(att.dtype), _rows(att, "attention maps"), int(hd), out.data_ptr(),
+          _out_rows(out, T, H * hd_out, "difference_join"), int(hd_out), T, int(H), int(per_group), int(vd), float(lam), float(eps),
+          float(out_scale), _stream())
 
 
 def softcap(x: torch.Tensor, cap: float) -> None:
@@ -587,7 +641,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
               hd: int, scale: float, window: int = 0, decode_max_keys: int = 0,
               cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None,
-              max_keys: int = 0, max_blocks: int = 0, key_ranges: int = 0, softcap: float = 0.0, sink: bool = False) -> None:
+              max_keys: int = 0, max_blocks: int = 0, key_ranges: int = 0, softcap: float = 0.0, sink: bool = False,
+              keep_first: int = 0, sink_values: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
     or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
     steps of sequences no longer than that: keys are then split across blocks.  With
@@ -599,9 +654,14 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     kernel cuts the keys of a row tile (0: chosen: more than one for few rows over many keys).  softcap > 0: scores are
     softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one more term of score 0, which
     carries no value (both served by the tcgen05 kernel of prompts, the warp kernels and the split-key kernels of single
-    tokens)."""
-    _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
+    tokens).  sink_values float32 [H]: the sink's score per head instead of 0 (implies sink; the score is taken as it is, not
+    scaled).  keep_first > 0 (with a window): the first keep_first keys of a sequence stay visible to every later query."""
+    _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, sink_values)
     T = q.shape[0]
+    if sink_values is not None:
+        _f32vec(sink_values, H, "attention sink scores")
+        sink = True
+    keep_first = int(keep_first) if window else 0
     if not q.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.dtype != q.dtype or k_pages.dtype != q.dtype:
         raise KernelError("attention: q must be contiguous [T, H*hd], q and out of the pages' type")
     out_ld = _out_rows(out, T, H * hd, "attention")
@@ -612,12 +672,13 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_decode", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(),
               slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
-              int(window or 0), int(decode_max_keys), out_ld, float(softcap), int(bool(sink)), _stream())
+              int(window or 0), int(decode_max_keys), out_ld, float(softcap), int(bool(sink)), keep_first, _p(sink_values),
+              _stream())
         return
     own_softmax = softcap > 0 or sink
     tiled = decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
         and hd in (64, 128) and not DISABLE_TILED_ATTENTION
-    if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
+    if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 and keep_first == 0 and sink_values is None \
             and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
         B = slots.numel()
         # few row tiles and many keys (a piece of a long prompt): the keys in ranges that run side by side
@@ -631,7 +692,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               out.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
               out_ld, int(max_blocks), int(n_split), _p(part_o), _p(part_ml), float(softcap), int(bool(sink)), _stream())
         return
-    if tiled and not own_softmax:
+    if tiled and not own_softmax and keep_first == 0:
         B = slots.numel()
         n_tiles = T // 64 + B
         chunk = ctypes.c_int(0)
@@ -648,7 +709,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         return
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),
-          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), out_ld, float(softcap), int(bool(sink)), _stream())
+          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), out_ld, float(softcap), int(bool(sink)), keep_first,
+          _p(sink_values), _stream())
 
 
 DISABLE_FUSED_DECODE_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_FUSED_DECODE_ATTENTION", "0")))
@@ -1045,12 +1107,15 @@ UNGATED_ACTS = ("relu_squared",)          # experts of one product: w_up [E, F, 
 
 
 def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32, weights: str = "sigmoid",
-              choice_bias: Optional[torch.Tensor] = None, n_identity: int = 0):
+              choice_bias: Optional[torch.Tensor] = None, n_identity: int = 0, sum_to: float = 0.0):
     """Routing of every row of logits (float32 [T, >= E], the first E columns): returns (ids [T*top] int32, weights
     [T*top] float32 = sigmoid of the chosen logits, or with weights "softmax" a softmax restricted to the picked logits,
     order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as tlc_moe_route describes them.  With weights "softmax_all"
     the scores are the softmax over all n_experts outputs, an expert is chosen by score + choice_bias and weighted by its
-    score.  The last n_identity of the n_experts outputs have no weights of an expert: no tile covers their pairs."""
+    score.  The last n_identity of the n_experts outputs have no weights of an expert: no tile covers their pairs.  sum_to > 0
+    (weights "softmax_all"): a token's weights are divided by their sum (+ 1e-20) and multiplied by sum_to."""
+    if sum_to and weights != "softmax_all":
+        raise KernelError("moe_route: weights normed to a sum go with weights 'softmax_all'")
     if weights not in ROUTE_WEIGHTS:
         raise KernelError(f"moe_route: unknown weighting '{weights}'; known: {sorted(ROUTE_WEIGHTS)}")
     _gpu(logits)
@@ -1069,7 +1134,7 @@ def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 3
     _gpu(choice_bias)
     _call("tlc_moe_route", logits.data_ptr(), _rows(logits, "router logits"), T, int(n_experts), int(top), ROUTE_WEIGHTS[weights],
           _p(choice_bias), int(n_identity), ids.data_ptr(),
-          wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), int(tile_rows), _stream())
+          wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), int(tile_rows), float(sum_to), _stream())
     return ids, wts, order, offsets, tile_off, int(tile_rows)
 
 
@@ -1174,12 +1239,19 @@ def wkv_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, decay_log: t
 
 # ---- queries, keys and output gate of an attention mixer ---------------------------------------------------
 def qk_rotate_norm(qkv: torch.Tensor, q_off: int, k_off: int, H: int, KV: int, stride: int, dim: int, inv_freq: torch.Tensor,
-                   interleaved: bool, norm_eps: Optional[float], positions: torch.Tensor) -> None:
+                   interleaved: bool, norm_eps: Optional[float], positions: torch.Tensor, q_weight: Optional[torch.Tensor] = None,
+                   k_weight: Optional[torch.Tensor] = None, pre_eps: float = 0.0, amplitude: float = 1.0) -> None:
     """In place on the float32 projection qkv [T, *] (H query heads from column q_off, KV key heads from k_off, heads
     `stride` values apart of which `dim` are in use): turns the pairs of the first 2 * len(inv_freq) dimensions of every
     head by position * inv_freq[i] (neighbours (2i, 2i+1) when interleaved, else (i, i + half)), then, with norm_eps not
-    None, divides the head by sqrt(mean(x^2) + norm_eps)."""
-    _gpu(qkv, inv_freq, positions)
+    None, divides the head by sqrt(mean(x^2) + norm_eps).  q_weight, k_weight (float32 [dim], both or neither): BEFORE the
+    rotation every query head becomes x / sqrt(mean(x^2) + pre_eps) * q_weight and every key head likewise with k_weight.
+    amplitude multiplies every cosine and sine."""
+    _gpu(qkv, inv_freq, positions, q_weight, k_weight)
+    _f32vec(q_weight, dim, "query norm weight")
+    _f32vec(k_weight, dim, "key norm weight")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qk_rotate_norm: the weights of the norm before the rotation come together")
     T = qkv.shape[0]
     _i32(positions, "positions")
     _f32vec(inv_freq, inv_freq.numel(), "rotation inv_freq")
@@ -1188,7 +1260,7 @@ def qk_rotate_norm(qkv: torch.Tensor, q_off: int, k_off: int, H: int, KV: int, s
         raise KernelError("qk_rotate_norm: a float32 projection that holds every head")
     _call("tlc_qk_rotate_norm", qkv.data_ptr(), ld, int(q_off), int(k_off), int(H), int(KV), int(stride), int(dim),
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(interleaved)), -1.0 if norm_eps is None else float(norm_eps),
-          positions.data_ptr(), T, _stream())
+          positions.data_ptr(), T, _p(q_weight), _p(k_weight), float(pre_eps), float(amplitude), _stream())
 
 
 GATES = {"sigmoid": 0, "silu": 1}
@@ -1212,16 +1284,24 @@ MAX_DELTA_KEY_DIM = 256   # delta_rule.cu: rows of a head's state that the threa
 
 
 def delta_prepare(qkv: torch.Tensor, q_off: int, k_off: int, G: int, dk: int, l2_eps: float, q_scale: float, proj: torch.Tensor,
-                  b_off: int, H: int, beta: torch.Tensor) -> None:
+                  b_off: int, H: int, beta: torch.Tensor, channel_decay: Optional[torch.Tensor] = None,
+                  A: Optional[torch.Tensor] = None) -> None:
     """In place on qkv (float32 [T, *], G query heads of dk values from q_off, G key heads from k_off): every head becomes
-    x / sqrt(sum(x^2) + l2_eps), the queries also times q_scale; beta [T, H] float32 = sigmoid(proj[:, b_off : b_off + H])."""
-    _gpu(qkv, proj, beta)
+    x / sqrt(sum(x^2) + l2_eps), the queries also times q_scale; beta [T, H] float32 = sigmoid(proj[:, b_off : b_off + H]).
+    channel_decay float32 [T, H * dk] with A float32 [H]: turned in place into exp(A[h] * softplus(x)), a decay per key
+    channel of every head."""
+    _gpu(qkv, proj, beta, channel_decay, A)
+    if channel_decay is not None:
+        if channel_decay.dtype != torch.float32 or tuple(channel_decay.shape) != (qkv.shape[0], H * dk) or A is None:
+            raise KernelError("delta_prepare: decays per channel are float32 [T, H * dk] and come with A [H]")
+        _f32vec(A, H, "delta_prepare A")
     T = qkv.shape[0]
     if qkv.dtype != torch.float32 or proj.dtype != torch.float32 or beta.dtype != torch.float32 or not beta.is_contiguous() \
             or tuple(beta.shape) != (T, H) or proj.shape[0] != T:
         raise KernelError("delta_prepare: float32 tensors, beta contiguous [T, H]")
     _call("tlc_delta_prepare", qkv.data_ptr(), _rows(qkv, "qkv"), int(q_off), int(k_off), int(G), int(dk), float(l2_eps),
-          float(q_scale), proj.data_ptr(), _rows(proj, "proj"), int(b_off), int(H), beta.data_ptr(), T, _stream())
+          float(q_scale), proj.data_ptr(), _rows(proj, "proj"), int(b_off), int(H), beta.data_ptr(), T, _p(channel_decay),
+          0 if channel_decay is None else _rows(channel_decay, "decays"), _p(A), _stream())
 
 
 def delta_rule_split(threads: int) -> None:
@@ -1231,17 +1311,21 @@ def delta_rule_split(threads: int) -> None:
 
 
 def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
-               step, y: torch.Tensor, H: int, G: int, dk: int, dv: int) -> None:
+               step, y: torch.Tensor, H: int, G: int, dk: int, dv: int, per_channel: bool = False) -> None:
     """The gated delta rule over every sequence's rows of the step, from its slot's state [n_slots, H, dk, dv] float32
     (zero at position 0; updated in place): M <- a M; w = b (v - M^T k); M <- M + k w^T; y = M^T q (a the decay, b the
-    write strength `beta`).  qkv float32
+    write strength `beta`; decay [T, H], or [T, H * dk] for a factor per key channel: M <- diag(a) M).  qkv float32
     [T, *] holds the prepared queries and keys (G heads of dk) and the values (H heads of dv); beta, decay float32 [T, H];
     y float32 [T, H*dv]."""
     _gpu(qkv, beta, decay, state, y)
     T = qkv.shape[0]
-    for t, n in ((beta, "beta"), (decay, "decay")):
+    if per_channel and (decay.dim() != 2 or decay.shape[1] != H * dk):
+        raise KernelError("delta_rule: decays per channel must be float32 [T, H * dk]")
+    for t, n in ((beta, "beta"),) + (() if per_channel else ((decay, "decay"),)):
         if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != (T, H):
             raise KernelError(f"delta_rule: {n} must be contiguous float32 [T, H]")
+    if per_channel and (decay.dtype != torch.float32 or decay.shape[0] != T):
+        raise KernelError("delta_rule: decays per channel must be float32 [T, H * dk]")
     if qkv.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
         raise KernelError("delta_rule: float32 inputs and a contiguous float32 state [n_slots, H, dk, dv]")
     if y.dtype != torch.float32:
@@ -1249,4 +1333,4 @@ def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torc
     ldy = _out_rows(y, T, H * dv, "delta_rule")
     _call("tlc_delta_rule", qkv.data_ptr(), _rows(qkv, "qkv"), int(q_off), int(k_off), int(v_off), beta.data_ptr(), decay.data_ptr(),
           state.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(), step.n_seqs, T, int(H),
-          int(G), int(dk), int(dv), y.data_ptr(), ldy, _stream())
+          int(G), int(dk), int(dv), y.data_ptr(), ldy, _rows(decay, "decays") if per_channel else 0, _stream())

@@ -48,6 +48,8 @@ class KVRequest:
     window: Optional[int] = None
     values: bool = True         # False: one row per position only (the "keys" pages); a mixer that derives its values
                                 # from the same row (a shared latent) asks for no second set of pages
+    keep_first: int = 0         # with a window: the first keep_first positions stay visible to every later query, so the
+                                # pages that hold them are never given back
 
 
 @dataclass(frozen=True)
@@ -204,7 +206,9 @@ class LayerSpec:
     shift) declares it like a mixer does.  A feed-forward without a norm of its own (ffn_norm None) runs in parallel with
     the mixers: it reads what the mixers read, h = mixer_norm(x), and x <- x + mixers(h) + ffn(h).  A norm named "none"
     in front of a sublayer means that it reads the stream itself.  mixer_join (a norm part with add_joined, "rmsnorm_mean")
-    says how several mixers' results become one where that is not their sum: x <- x + out_norm(join(mixer_i(h)))."""
+    says how several mixers' results become one where that is not their sum: x <- x + out_norm(join(mixer_i(h))).
+    parallel: the feed-forward HAS a norm of its own but applies it to the layer's input, like the mixers do theirs:
+    x <- x + mixers(mixer_norm(x)) + ffn(ffn_norm(x)), both norms of the same x."""
     mixer_norm: PartSpec
     mixers: Tuple[PartSpec, ...]
     ffn_norm: Optional[PartSpec]
@@ -212,6 +216,7 @@ class LayerSpec:
     mixer_out_norm: Optional[PartSpec] = None
     ffn_out_norm: Optional[PartSpec] = None
     mixer_join: Optional[PartSpec] = None
+    parallel: bool = False
 
 
 @dataclass(frozen=True)
@@ -222,10 +227,12 @@ class LayerRun:
     entry of the run order (by its index) whose cache this entry reads instead, without
     storing into it.  ``kv_cache`` names an entry whose keys and values (only those) this entry
     reads without storing, while it keeps fixed-size state of its own: a layer that attends over
-    what another layer cached."""
+    what another layer cached.  ``add`` = (table, row) names a learned table of the model ([rows, width]) whose row is added
+    to the residual stream right before this entry runs (a range of layers that repeats marks each pass this way)."""
     layer: int
     cache: Optional[int] = None
     kv_cache: Optional[int] = None
+    add: Optional[Tuple[str, int]] = None
 
     @property
     def writes(self) -> bool:

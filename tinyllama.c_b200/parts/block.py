@@ -81,8 +81,10 @@ class Block(Part):
         self.mixer_join = spec.mixer_join.build() if spec.mixer_join is not None else None
         if self.mixer_join is not None and not self.mixers:
             raise ValueError("a join of the mixers' results needs mixers")
-        # a feed-forward without a norm of its own is a parallel branch: it reads the mixers' normed input
-        self.parallel_ffn = self.ffn is not None and self.ffn_norm is None
+        # a feed-forward without a norm of its own is a parallel branch: it reads the mixers' normed input; so is one
+        # whose own norm is applied to the layer's input (LayerSpec.parallel)
+        self.parallel_ffn = self.ffn is not None and (self.ffn_norm is None or bool(spec.parallel))
+        self.own_parallel_norm = self.parallel_ffn and self.ffn_norm is not None
         if self.parallel_ffn and (not self.mixers or self.ffn_out_norm is not None or self.mixer_out_norm is not None):
             raise ValueError("a feed-forward without a norm of its own runs beside the mixers on their normed input: the layer "
                              "needs mixers and takes no output norms")
@@ -220,7 +222,22 @@ class Block(Part):
         return bool(self.parallel_ffn and PARALLEL_FFN and x32.is_cuda and (step.max_new == 1 or PARALLEL_FFN_PROMPTS)
                     and hasattr(self.ffn, "forward_parts") and hasattr(self.ffn, "add_parts"))
 
-    def _two_branches(self, normed: torch.Tensor, x32: torch.Tensor, run_mixers) -> None:
+    def _parallel_inputs(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache):
+        """(what the mixers read, what a parallel feed-forward reads): one normed copy of the layer's input, or, where the
+        feed-forward has a norm of its own, two; norms that share their statistics (pairs_with) make both in one kernel."""
+        if not self.own_parallel_norm:
+            normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
+            return normed, normed
+        pairs = getattr(self.mixer_norm, "pairs_with", None)
+        if pairs is not None and pairs(self.ffn_norm):
+            normed = scratch_buf("block.normed", x32.shape, self.dtype, x32.device)
+            ffn_in = scratch_buf("block.ffn_normed", x32.shape, self.dtype, x32.device)
+            self.mixer_norm.forward_pair(x32, normed, self.ffn_norm, ffn_in)
+            return normed, ffn_in
+        return (self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache),
+                self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache))
+
+    def _two_branches(self, normed: torch.Tensor, x32: torch.Tensor, run_mixers, ffn_in: Optional[torch.Tensor] = None) -> None:
         """A parallel layer on two streams (under stream capture: two branches of the graph): the mixers, which add
         their outputs into the residual stream, and the feed-forward's terms; the terms are added after the branches have
         met, on the current stream, so the order of the sums is fixed.  run_mixers(): launches the mixers on whatever
@@ -239,12 +256,12 @@ class Block(Part):
             if PARALLEL_FFN == 1:
                 run_mixers()
             else:
-                terms = self.ffn.forward_parts(normed)
+                terms = self.ffn.forward_parts(normed if ffn_in is None else ffn_in)
             self._ffn_done.record(side)
         finally:
             torch.cuda.set_stream(main)
         if PARALLEL_FFN == 1:
-            terms = self.ffn.forward_parts(normed)
+            terms = self.ffn.forward_parts(normed if ffn_in is None else ffn_in)
         else:
             run_mixers()
         main.wait_event(self._ffn_done)
@@ -334,14 +351,15 @@ class Block(Part):
                     m.forward(x32 if reads[i] else normed, step, cache, y)
             self.mixer_out_norm.add_normed(y, x32, copy=copy)
         elif self.mixers:
-            normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
+            normed, ffn_in = self._parallel_inputs(x32, step, cache) if self.parallel_ffn \
+                else (self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache), None)
             if self._beside(x32, step):
-                self._two_branches(normed, x32, lambda: self._run_mixers(normed, x32, step, cache))
+                self._two_branches(normed, x32, lambda: self._run_mixers(normed, x32, step, cache), ffn_in)
                 return False
             self._run_mixers(normed, x32, step, cache)
         if self.parallel_ffn:
             # h was normed before the mixers added anything; the sum x + mixers(h) + ffn(h) forms in the residual stream
-            self.ffn.forward(normed, x32)
+            self.ffn.forward(ffn_in, x32)
             return False
         if self.ffn is not None:
             return self._feed_forward(x32, step, cache, copy_for_next)

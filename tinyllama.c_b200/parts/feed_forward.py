@@ -75,6 +75,38 @@ class SwiGLU(Part):
 
 
 
+@register_feed_forward("mlp")
+class DenseFeedForward(Part):
+    """A feed-forward without a gate: d = W_down act(W_up x), act the square of max(., 0) ("relu_squared").  Two products
+    with the activation between them (32-bit in, activation type out)."""
+
+    def __init__(self, hidden: int, intermediate: int, names: Dict[str, str], act: str = "relu_squared"):
+        """names: tensor names of up and down."""
+        if act not in ("relu_squared",):
+            raise ValueError(f"feed-forward: unknown activation '{act}' of a feed-forward without a gate; known: ['relu_squared']")
+        self.hidden, self.F, self.act = int(hidden), int(intermediate), act
+        self.up = StackedLinear(hidden)
+        self.up.add(names["up"], self.F)
+        self.down = StackedLinear(self.F)
+        self.down.add(names["down"], hidden)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return self.up.weight_specs() + self.down.weight_specs()
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.up.bind(tensors, dtype, device)
+        self.down.bind(tensors, dtype, device)
+
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        """Adds the result into `residual` (float32 [T, D]), or overwrites it with accumulate False."""
+        T = normed.shape[0]
+        u = scratch_buf("mlp.up", (T, self.F), torch.float32, normed.device)
+        self.up.forward(normed, u)
+        act = scratch_buf("mlp.act", (T, self.F), normed.dtype, normed.device)
+        ops.convert(u, act, self.act)
+        self.down.forward(act, residual, accumulate=accumulate)
+
+
 @register_feed_forward("moe")
 class MoEFeedForward(Part):
     """Mixture of experts.  By default, with a sigmoid router:
@@ -103,8 +135,12 @@ class MoEFeedForward(Part):
     def __init__(self, hidden: int, n_experts: int, top: int, expert_ff: int, router_name: str, expert_names: Dict[str, str],
                  shared: Optional[PartSpec] = None, shared_gate_name: Optional[str] = None, router_bias_name: Optional[str] = None,
                  weights: str = "sigmoid", weight_on: str = "input", act: str = "silu", limit: float = 0.0, alpha: float = 1.0,
-                 choice_bias_name: Optional[str] = None, n_identity: int = 0):
-        """expert_names: patterns of gate, up, down with {e} for the expert's index."""
+                 choice_bias_name: Optional[str] = None, n_identity: int = 0, weights_sum_to: float = 0.0):
+        """expert_names: patterns of gate, up, down with {e} for the expert's index.  weights_sum_to > 0 (weights
+        "softmax_all"): a token's weights are the chosen scores divided by their sum (+ 1e-20) times this number."""
+        self.weights_sum_to = float(weights_sum_to)
+        if self.weights_sum_to < 0 or (self.weights_sum_to and weights != "softmax_all"):
+            raise ValueError("moe: weights normed to a sum go with weights 'softmax_all' and a positive sum")
         if weights not in ops.ROUTE_WEIGHTS or weight_on not in ("input", "output") or act not in ops.MOE_ACTS:
             raise ValueError(f"moe: unknown weighting '{weights}', weight placement '{weight_on}' or activation '{act}'")
         if act == "swish_clamped" and not limit > 0:
@@ -184,7 +220,7 @@ class MoEFeedForward(Part):
         logits = scratch_buf("moe.logits", (T, n_logits), torch.float32, dev)
         ops.linear(normed, self.router, logits, None, self.router_bias)
         routing = ops.moe_route(logits, self.n_out, self.top, ops.moe_tile_rows(normed, self.w_gate_up, self.dtype, self.top, self.F),
-                                self.weights, self.choice_bias, self.n_identity)
+                                self.weights, self.choice_bias, self.n_identity, self.weights_sum_to)
         act = scratch_buf("moe.act", (T * self.top, self.F), self.dtype, dev)
         parts = scratch_buf("moe.parts", (T, self.top, self.hidden), torch.float32, dev)
         ops.moe_experts(normed, self.w_gate_up, self.w_down, routing, self.top, act, parts, self.act, self.weight_on, self.limit,

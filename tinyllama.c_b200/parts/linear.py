@@ -43,27 +43,52 @@ class StackedLinear:
         self.colbias: Optional[torch.Tensor] = None
 
     def add(self, weight_name: str, rows: int, bias_name: Optional[str] = None, in_scale: float = 1.0,
-            out_scale=1.0, heads: Optional[tuple] = None) -> int:
+            out_scale=1.0, heads: Optional[tuple] = None, gather: Optional[tuple] = None) -> int:
         """Adds `rows` output rows; returns their first column in the stacked output.
         y = ((x * in_scale) W^T + bias) * out_scale, out_scale a number or one value per row.
         heads = (n, have, want): the stored matrix has n * have rows, n heads of `have`; the projection gives every head
-        `want` >= have outputs (rows = n * want), the extra ones zero."""
+        `want` >= have outputs (rows = n * want), the extra ones zero (so is the bias there).
+        gather = (stored rows, index): the stored matrix (and bias) has that many rows and the projection's row i is the stored
+        row index[i] (before any padding of heads): rows in another order, or rows that serve twice."""
         off = self.out_features
+        if gather is not None:
+            gather = (int(gather[0]), tuple(int(i) for i in gather[1]))
+            if not gather[1] or min(gather[1]) < 0 or max(gather[1]) >= gather[0]:
+                raise ValueError(f"gathered rows must index the {gather[0]} stored rows")
         if heads is not None:
             heads = tuple(int(v) for v in heads)
-            if heads[0] * heads[2] != int(rows) or heads[1] > heads[2] or bias_name:
-                raise ValueError(f"padded heads {heads} do not make {rows} rows (and take no bias)")
+            if heads[0] * heads[2] != int(rows) or heads[1] > heads[2]:
+                raise ValueError(f"padded heads {heads} do not make {rows} rows")
+        made = len(gather[1]) if gather is not None else None
+        if made is not None and made != (heads[0] * heads[1] if heads is not None else int(rows)):
+            raise ValueError(f"{made} gathered rows do not make the projection's {rows} rows")
         self.segments.append(dict(w=weight_name, b=bias_name, rows=int(rows), in_scale=float(in_scale),
-                                  out_scale=out_scale, off=off, heads=heads))
+                                  out_scale=out_scale, off=off, heads=heads, gather=gather))
         return off
 
     def _stored_shape(self, seg: dict) -> tuple:
         rows = seg["rows"] if not seg.get("heads") else seg["heads"][0] * seg["heads"][1]
+        if seg.get("gather"):
+            rows = seg["gather"][0]
         cols = self.in_features if not self.in_heads else self.in_heads[0] * self.in_heads[1]
         return (rows, cols)
 
+    @staticmethod
+    def _rows_laid_out(seg: dict, m: torch.Tensor) -> torch.Tensor:
+        """Stored rows (of a matrix, or a bias as a column) -> the projection's rows: gathered, then heads padded with zeros."""
+        if seg.get("gather"):
+            m = m[torch.tensor(seg["gather"][1], dtype=torch.long, device=m.device)]
+        if seg.get("heads"):
+            n, have, want = seg["heads"]
+            full = m.new_zeros((n, want) + tuple(m.shape[1:]))
+            full[:, :have] = m.reshape((n, have) + tuple(m.shape[1:]))
+            m = full.reshape((n * want,) + tuple(m.shape[1:]))
+        return m
+
     def _laid_out(self, seg: dict, m: torch.Tensor) -> torch.Tensor:
-        """The stored matrix with zero rows / columns where heads are padded."""
+        """The stored matrix with its rows gathered and zero rows / columns where heads are padded."""
+        if seg.get("gather"):
+            m = m[torch.tensor(seg["gather"][1], dtype=torch.long, device=m.device)]
         if seg.get("heads"):
             n, have, want = seg["heads"]
             full = m.new_zeros((n, want, m.shape[1]))
@@ -85,7 +110,7 @@ class StackedLinear:
         for s in self.segments:
             specs.append(WeightSpec(s["w"], self._stored_shape(s), "normal"))
             if s["b"]:
-                specs.append(WeightSpec(s["b"], (s["rows"],), "normal"))
+                specs.append(WeightSpec(s["b"], (self._stored_shape(s)[0],), "normal"))
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
@@ -108,7 +133,7 @@ class StackedLinear:
                 else torch.full((s["rows"],), float(osc), dtype=torch.float64)
             scale[sl] = osc * s["in_scale"]
             if s["b"]:
-                bias[sl] = tensors[s["b"]].to(device="cpu", dtype=torch.float64) * osc
+                bias[sl] = self._rows_laid_out(s, tensors[s["b"]].to(device="cpu", dtype=torch.float64)) * osc
                 any_bias = True
             if bool((scale[sl] != 1.0).any()):
                 any_scale = True

@@ -18,6 +18,13 @@ at position 0 starts from zeros); everything between the projections and the out
 
 The six projections of h are one product.  The convolution (with the decay beside it: dt = softplus(W_a h + dt_bias),
 a = exp(dt * -exp(A_log))) is the kernel that serves every short convolution of the library.
+
+Options.  decay="channel": a factor per head AND key channel, a [H, dk] = exp(-exp(A_log_h) * softplus(W_a2 (W_a1 h) +
+dt_bias)) with a low-rank pair of matrices and dt_bias of H * dk values; the state's rows are decayed each by its own
+factor, M <- diag(a) M.  gate_rank: the gate's projection is a low-rank pair as well, W_g2 (W_g1 h).  gate="sigmoid":
+the read-out is gated by sigmoid(.) instead of silu(.).  The ranks are no keys of a configuration: the stored matrices
+give them (shapes_from).  The first matrices of both pairs are stacked with the other projections of h; the hidden rows
+are rounded to the activation type and the two second products follow (dt_bias in the epilogue of the decay's).
 """
 from __future__ import annotations
 
@@ -33,9 +40,18 @@ from ..linear import StackedLinear
 @register_mixer("delta")
 class DeltaMixer(Part):
     def __init__(self, hidden: int, n_heads: int, n_qk_heads: int, key_dim: int, v_dim: int, conv_taps: int, eps: float,
-                 names: Dict[str, str], l2_eps: float = 1e-6, q_scale: Optional[float] = None, cache_key: str = "delta"):
-        """names: tensor names of q, k, v (their convolutions are these names + '.conv'), b, a, A_log, dt_bias, norm, g, o.
-        eps: of the output norm."""
+                 names: Dict[str, str], l2_eps: float = 1e-6, q_scale: Optional[float] = None, cache_key: str = "delta",
+                 decay: str = "head", gate: str = "silu", low_rank_gate: bool = False, decay_rank: Optional[int] = None,
+                 gate_rank: Optional[int] = None):
+        """names: tensor names of q, k, v (their convolutions are these names + '.conv'), b, a, A_log, dt_bias, norm, g, o;
+        with decay "channel" a1 and a2 instead of a, with low_rank_gate g1 and g2 instead of g.  eps: of the output norm.
+        decay_rank, gate_rank: the hidden widths of the low-rank pairs for a model that is yet to be written (a stored
+        model's matrices give them)."""
+        if decay not in ("head", "channel") or gate not in ("silu", "sigmoid"):
+            raise ValueError(f"delta: decay '{decay}' (head or channel), gate '{gate}' (silu or sigmoid)")
+        self.decay_kind, self.gate_kind, self.low_rank_gate = decay, gate, bool(low_rank_gate)
+        self.decay_rank = int(decay_rank) if decay_rank else None
+        self.gate_rank = int(gate_rank) if gate_rank else None
         self.hidden, self.H, self.G, self.dk, self.dv, self.K = (int(hidden), int(n_heads), int(n_qk_heads), int(key_dim),
                                                                  int(v_dim), int(conv_taps))
         if self.H % self.G:
@@ -51,23 +67,55 @@ class DeltaMixer(Part):
         self.names, self.cache_key = dict(names), cache_key
         n = self.names
         self.Cd = 2 * self.G * self.dk + self.H * self.dv          # channels of the convolution: q | k | v
+        self.o = StackedLinear(self.H * self.dv)
+        self.o.add(n["o"], hidden)
+        self.dtype = None
+        self._lay_out()
+
+    def _lay_out(self) -> None:
+        """The stacked projection of h (its widths depend on the ranks of the low-rank pairs)."""
+        n, hidden = self.names, self.hidden
+        default = max(8, hidden // 16)
+        self.ra = (self.decay_rank or default) if self.decay_kind == "channel" else 0
+        self.rg = (self.gate_rank or default) if self.low_rank_gate else 0
         self.proj = StackedLinear(hidden)
         self.q_off = self.proj.add(n["q"], self.G * self.dk)
         self.k_off = self.proj.add(n["k"], self.G * self.dk)
         self.v_off = self.proj.add(n["v"], self.H * self.dv)
-        self.a_off = self.proj.add(n["a"], self.H)
         self.b_off = self.proj.add(n["b"], self.H)
-        self.g_off = self.proj.add(n["g"], self.H * self.dv)
-        self.o = StackedLinear(self.H * self.dv)
-        self.o.add(n["o"], hidden)
-        self.dtype = None
+        # what comes last is what the second products read: the hidden rows of the low-rank pairs side by side
+        self.a_off = self.proj.add(n["a1"], self.ra) if self.ra else self.proj.add(n["a"], self.H)
+        self.g_off = self.proj.add(n["g1"], self.rg) if self.rg else self.proj.add(n["g"], self.H * self.dv)
+        self.a2 = self.g2 = None
+        if self.ra:
+            self.a2 = StackedLinear(self.ra)
+            self.a2.add(n["a2"], self.H * self.dk, n["dt_bias"])      # dt_bias joins in the product's epilogue
+        if self.rg:
+            self.g2 = StackedLinear(self.rg)
+            self.g2.add(n["g2"], self.H * self.dv)
+
+    def shapes_from(self, shapes: Dict[str, tuple]) -> None:
+        """The hidden widths of the low-rank pairs are no keys of the configuration: the stored matrices give them."""
+        n = self.names
+        if self.decay_kind == "channel" and n["a1"] in shapes:
+            self.decay_rank = int(shapes[n["a1"]][0])
+        if self.low_rank_gate and n["g1"] in shapes:
+            self.gate_rank = int(shapes[n["g1"]][0])
+        self._lay_out()
 
     def weight_specs(self) -> List[WeightSpec]:
         n = self.names
-        return self.proj.weight_specs() + self.o.weight_specs() + [
+        specs = self.proj.weight_specs() + self.o.weight_specs() + [
             WeightSpec(n["q"] + ".conv", (self.G * self.dk, self.K), "conv"), WeightSpec(n["k"] + ".conv", (self.G * self.dk, self.K), "conv"),
             WeightSpec(n["v"] + ".conv", (self.H * self.dv, self.K), "conv"), WeightSpec(n["A_log"], (self.H,), "a_log"),
-            WeightSpec(n["dt_bias"], (self.H,), "dt_bias"), WeightSpec(n["norm"], (self.dv,), "ones")]
+            WeightSpec(n["norm"], (self.dv,), "ones")]
+        if self.a2 is not None:
+            specs += [WeightSpec(n["a2"], (self.H * self.dk, self.ra)), WeightSpec(n["dt_bias"], (self.H * self.dk,), "dt_bias")]
+        else:
+            specs.append(WeightSpec(n["dt_bias"], (self.H,), "dt_bias"))
+        if self.g2 is not None:
+            specs += self.g2.weight_specs()
+        return specs
 
     def cache_requests(self) -> list:
         return [StateRequest(self.cache_key + ".conv", (self.K - 1, self.Cd)),
@@ -82,6 +130,10 @@ class DeltaMixer(Part):
                              device)
         self.A = (-torch.exp(tensors[n["A_log"]].to(torch.float32))).to(device).contiguous()      # decay = exp(dt * A)
         self.dt_bias = to_vec(tensors[n["dt_bias"]], device)
+        for second in (self.a2, self.g2):
+            if second is not None:
+                second.bind(tensors, dtype, device)
+        self._none = torch.zeros(0, dtype=torch.float32, device=device)
         self.norm_w = to_vec(tensors[n["norm"]], device).repeat(self.H).contiguous()              # one weight for every head
 
     def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor,
@@ -94,15 +146,34 @@ class DeltaMixer(Part):
         proj = new("proj", (T, self.proj.out_features), f32)
         self.proj.forward(normed, proj)
         qkv = new("qkv", (T, self.Cd), f32)
-        dt, decay = new("dt", (T, self.H), f32), new("decay", (T, self.H), f32)
-        ops.mamba_conv(proj, self.q_off, self.a_off, self.conv_w, None, self.dt_bias, self.A, cache.state[self.cache_key + ".conv"],
-                       step.cu_seqlens, step.row_seq, step.slots, step.start_pos, qkv, dt, decay, step.max_new == 1, False,
-                       len(step.host_start) == step.n_seqs and not any(step.host_start))
+        fresh = len(step.host_start) == step.n_seqs and not any(step.host_start)
+        channel = self.decay_kind == "channel"
+        if channel:            # the convolution alone; the decays come from the second product of their pair
+            none = self._none.view(T, 0) if T else self._none
+            ops.mamba_conv(proj, self.q_off, self.a_off, self.conv_w, None, self._none, self._none, cache.state[self.cache_key + ".conv"],
+                           step.cu_seqlens, step.row_seq, step.slots, step.start_pos, qkv, none, none, step.max_new == 1, False, fresh)
+        else:
+            dt, decay = new("dt", (T, self.H), f32), new("decay", (T, self.H), f32)
+            ops.mamba_conv(proj, self.q_off, self.a_off, self.conv_w, None, self.dt_bias, self.A, cache.state[self.cache_key + ".conv"],
+                           step.cu_seqlens, step.row_seq, step.slots, step.start_pos, qkv, dt, decay, step.max_new == 1, False, fresh)
+        gate = proj[:, self.g_off:self.g_off + self.H * self.dv]
+        if self.ra or self.rg:
+            # the hidden rows of the low-rank pairs, side by side at the end of the projection, in the activation type
+            hidden = new("hidden", (T, self.ra + self.rg), self.dtype)
+            first = self.a_off if self.ra else self.g_off
+            ops.convert(proj[:, first:first + self.ra + self.rg], hidden)
+            if self.ra:
+                decay = new("decay", (T, self.H * self.dk), f32)
+                self.a2.forward(hidden[:, :self.ra], decay)
+            if self.rg:
+                gate = new("gate", (T, self.H * self.dv), f32)
+                self.g2.forward(hidden[:, self.ra:], gate)
         beta = new("beta", (T, self.H), f32)
-        ops.delta_prepare(qkv, self.q_off, self.k_off, self.G, self.dk, self.l2_eps, self.q_scale, proj, self.b_off, self.H, beta)
+        ops.delta_prepare(qkv, self.q_off, self.k_off, self.G, self.dk, self.l2_eps, self.q_scale, proj, self.b_off, self.H, beta,
+                          decay if channel else None, self.A if channel else None)
         y = new("y", (T, self.H * self.dv), f32)
         ops.delta_rule(qkv, self.q_off, self.k_off, self.v_off, beta, decay, cache.state[self.cache_key + ".state"], step, y,
-                       self.H, self.G, self.dk, self.dv)
+                       self.H, self.G, self.dk, self.dv, per_channel=channel)
         gated = new("gated", (T, self.H * self.dv), self.dtype)
-        ops.gated_rmsnorm(y, proj[:, self.g_off:self.g_off + self.H * self.dv], self.norm_w, self.eps, self.H, True, gated)
+        ops.gated_rmsnorm(y, gate, self.norm_w, self.eps, self.H, True, gated, gate=self.gate_kind)
         self.o.forward(gated, residual, accumulate=accumulate)

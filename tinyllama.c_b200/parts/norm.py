@@ -41,6 +41,34 @@ class RMSNorm(Part):
         ops.rmsnorm_add(parts, self.weight, self.eps, residual, extra, gate, gate_sigmoid=True, copy=copy)
 
 
+@register_norm("layernorm")
+class LayerNorm(Part):
+    """Layer norm with a weight and no bias: (x - mean(x)) / sqrt(var(x) + eps) * w, var the mean of the squared deviations.
+    Statistics are 32-bit.  Two layer norms of one width and eps applied to the SAME rows (a layer whose mixer and
+    feed-forward each norm the layer's input) share the statistics: forward_pair writes both results in one pass."""
+
+    def __init__(self, width: int, eps: float, weight_name: str):
+        self.width, self.eps, self.weight_name = int(width), float(eps), weight_name
+        self.weight: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.weight_name, (self.width,), "ones")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.weight = to_vec(tensors[self.weight_name], device)
+
+    def forward(self, x32: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        ops.layernorm(x32, self.weight, self.eps, out, rows)
+        return out
+
+    def pairs_with(self, other) -> bool:
+        return type(other) is LayerNorm and other.width == self.width and other.eps == self.eps
+
+    def forward_pair(self, x32: torch.Tensor, out: torch.Tensor, other: "LayerNorm", out_other: torch.Tensor) -> None:
+        """out = this norm of x32, out_other = `other`'s norm of the same rows (pairs_with(other) must hold)."""
+        ops.layernorm(x32, self.weight, self.eps, out, None, other.weight, out_other)
+
+
 @register_norm("rmsnorm_shift")
 class RMSNormShift(RMSNorm):
     """RMSNorm followed by a token shift: with n[t] the normed row, the result is n[t] + (n[t-1] - n[t]) * mix, mix a
