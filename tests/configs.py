@@ -244,3 +244,106 @@ def sogazen_random(seed: int) -> dict:
             _s_right(heads, vdim, pick(8, 16, 32, 40), groups, ng, pick(1, 2, 3, 4, 6)), mlp))
     return dict(architecture="Sogazen", vocab=pick(50, 131, 300), width=pick(32, 44, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)),
                 logit_softcap=pick(5.0, 30.0), layers=layers)
+
+
+# ---- Kimutar ---------------------------------------------------------------------------------------------------
+def _k_rot(base, dims, **scaling):
+    rot = dict(base=base, dims=dims)
+    if scaling:
+        rot["scaling"] = scaling
+    return rot
+
+
+def _k_diff(heads, kv_heads, dim, vdim, scale, diff, rot, mlp):
+    return dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, diff=diff, rot=rot), mlp=mlp)
+
+
+def _k_window(heads, kv_heads, dim, vdim, scale, rot, size, keep_first, mlp):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, rot=rot)
+    if size:
+        m["mask"] = dict(size=size, keep_first=keep_first)
+    return dict(type="attention_2", mixer=m, mlp=mlp)
+
+
+def _k_delta(heads, kv_heads, dim, vdim, conv, decay_rank, gate_rank, mlp):
+    return dict(type="channel_delta", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv, decay_rank=decay_rank,
+                                                 gate_rank=gate_rank), mlp=mlp)
+
+
+def _k_moe(experts, top, scale, ff, shared=None):
+    mlp = dict(kind="moe", router=dict(experts=experts, top=top, scale=scale), expert=dict(ff=ff))
+    if shared:
+        mlp["shared"] = dict(ff=shared)
+    return mlp
+
+
+def _k_dense(ff):
+    return dict(kind="dense", ff=ff)
+
+
+# A: a recurrent layer first, inside the repeated range (three passes from layer 0); a width that is no multiple of 8; two
+# maps with keys wider than values and a third of the dimensions rotated along a ramp, and two maps without any rotation; a
+# window of 5 keys that keeps 2 and one of 70 that keeps none; six query heads on one key/value head; values wider than keys
+# under biases; one query/key head for two value heads of the delta rule, two taps; a layer without feed-forward; experts
+# with and without a shared one, every expert chosen
+KIMUTAR_A = dict(architecture="Kimutar", vocab=150, width=52, norm=dict(eps=1e-5), loop=dict(start=0, stop=2, times=3), layers=[
+    _k_delta(4, 2, 8, 12, 2, 5, 7, _k_moe(4, 2, 1.5, 20, shared=16)),
+    _k_diff(4, 2, 24, 16, 0.3, 0.2, _k_rot(100.0, 8, factor=4.0, original=64, fast=8.0, slow=2.0), _k_dense(40)),
+    _k_window(3, 3, 16, 24, 0.4, _k_rot(10000.0, 16, factor=3.0, low=1.0, high=5.0, original=50), 5, 2, None),
+    _k_window(6, 1, 20, 20, 0.2, _k_rot(500.0, 6), 70, 0, _k_moe(2, 2, 0.7, 12)),
+    _k_diff(2, 2, 16, 16, 0.25, 0.45, _k_rot(10000.0, 0), _k_moe(3, 1, 3.0, 24, shared=8)),
+])
+
+# B: heads of 64 (the tcgen05 attention of prompts and the one-kernel attention of single tokens): a window of 33 keys that
+# keeps 3 and a sink, keys narrower than values with a window of 100 that keeps 70 (more than a page), two maps of 64 half
+# rotated; the delta rule with keys of 72 values (five rows a thread) and four taps; the repeated range in the middle, twice;
+# no window at all in the last layer
+KIMUTAR_B = dict(architecture="Kimutar", vocab=97, width=64, norm=dict(eps=1e-6), loop=dict(start=1, stop=3, times=2), layers=[
+    _k_window(2, 1, 64, 64, 0.11, _k_rot(1000000.0, 64, factor=8.0, low=1.0, high=4.0, original=128), 33, 3, _k_dense(96)),
+    _k_delta(2, 1, 72, 40, 4, 12, 9, _k_moe(5, 3, 2.5, 24, shared=32)),
+    _k_diff(2, 1, 64, 64, 0.13, 0.3, _k_rot(50000.0, 32, factor=2.0, original=100, fast=16.0, slow=1.0), _k_moe(3, 2, 1.0, 16)),
+    _k_window(4, 2, 32, 64, 0.2, _k_rot(10000.0, 32, factor=2.0, low=2.0, high=3.0, original=40), 100, 70, None),
+    _k_window(2, 2, 64, 64, 0.12, _k_rot(300.0, 16), None, 0, _k_dense(40)),
+])
+
+KIMUTAR = {"KA": KIMUTAR_A, "KB": KIMUTAR_B}
+
+
+def kimutar_random(seed: int) -> dict:
+    """A Kimutar configuration drawn from `seed`: 2 to 5 layers of the three kinds in any order, a repeated range or none, with
+    head counts, sizes, rotated dimensions, scalings, windows, kept keys, taps, ranks, experts and constants all drawn."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    pick = lambda *v: v[int(rng.integers(len(v)))]
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        r = rng.random()
+        if r < 0.2:
+            mlp = None
+        elif r < 0.45:
+            mlp = _k_dense(pick(8, 20, 36, 64))
+        else:
+            experts = pick(1, 2, 3, 5, 8)
+            mlp = _k_moe(experts, int(rng.integers(1, min(experts, 4) + 1)), pick(0.5, 1.0, 2.5), pick(8, 12, 24, 40), shared=pick(None, 8, 24))
+        kind = pick("attention", "attention_2", "channel_delta")
+        kv = pick(1, 2, 3)
+        heads = kv * pick(1, 2, 3, 5)
+        if kind == "channel_delta":
+            layers.append(_k_delta(heads, kv, pick(4, 8, 20, 32, 40, 64), pick(8, 12, 32, 40), pick(1, 2, 3, 4, 6), pick(3, 8, 16), pick(2, 8, 24), mlp))
+            continue
+        dim, vdim = pick(8, 16, 24, 32, 64), pick(8, 16, 32, 64)
+        dims = pick(0, 2, dim // 4 * 2, dim)
+        scale = float(dim ** -0.5 * rng.uniform(0.5, 2.0))
+        if kind == "attention":
+            sc = pick(None, dict(factor=pick(2.0, 6.0), original=pick(32, 100), fast=pick(8.0, 32.0), slow=pick(1.0, 2.0)))
+            layers.append(_k_diff(heads, kv, dim, vdim, scale, pick(0.1, 0.3, 0.6), _k_rot(pick(50.0, 10000.0, 250000.0), dims, **(sc or {})), mlp))
+        else:
+            sc = pick(None, dict(factor=pick(2.0, 8.0), original=pick(32, 100), low=pick(1.0, 2.0), high=pick(3.0, 4.0)))
+            size = pick(None, 1, 7, 40, 64, 90)
+            layers.append(_k_window(heads, kv, dim, vdim, scale, _k_rot(pick(50.0, 10000.0, 250000.0), dims, **(sc or {})), size,
+                                    pick(0, 1, 4, 66) if size else 0, mlp))
+    cfg = dict(architecture="Kimutar", vocab=pick(50, 131, 300), width=pick(32, 44, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)), layers=layers)
+    if rng.random() < 0.7:
+        start = int(rng.integers(0, len(layers)))
+        cfg["loop"] = dict(start=start, stop=int(rng.integers(start + 1, len(layers) + 1)), times=pick(1, 2, 3))
+    return cfg

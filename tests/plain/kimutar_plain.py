@@ -124,6 +124,15 @@ def rotate_neighbours(x, pos, freq):
     return x
 
 
+def _frequencies(rot, scaled):
+    """(frequencies, amplitude of cosines and sines) of a mixer's 'rot': none rotated, plain, or stretched by `scaled`."""
+    if not rot["dims"]:
+        return np.zeros(0), 1.0
+    if rot.get("scaling") is None:
+        return plain_frequencies(rot["base"], rot["dims"]), 1.0
+    return scaled(rot["base"], rot["dims"], rot["scaling"])
+
+
 # ---- attention ------------------------------------------------------------------------------------------------------
 def visible(i, j, size=None, keep_first=0):
     """Whether query position i sees key position j: causal, and with a window only the last `size` positions and the
@@ -152,7 +161,7 @@ def difference_attention(h, W, p, m, eps, rnd=_same):
     T = h.shape[0]
     H, G, d, dv, diff = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["diff"]
     pos = np.arange(T)
-    freq, grow = ramp_frequencies(m["rot"]["base"], m["rot"]["dims"], m["rot"]["scaling"]) if m["rot"]["dims"] else (np.zeros(0), 1.0)
+    freq, grow = _frequencies(m["rot"], ramp_frequencies)
     q = (h @ W[p + "q"].T).reshape(T, H * 2, d)
     k = (h @ W[p + "k"].T).reshape(T, G * 2, d)
     v = rnd(h @ W[p + "v"].T).reshape(T, G, dv)
@@ -173,7 +182,8 @@ def window_attention(h, W, p, m, eps, rnd=_same):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     pos = np.arange(T)
-    freq = band_frequencies(m["rot"]["base"], m["rot"]["dims"], m["rot"]["scaling"]) if m["rot"]["dims"] else np.zeros(0)
+    freq, _ = _frequencies(m["rot"], lambda base, dims, sc: (band_frequencies(base, dims, sc), 1.0))
+    mask = m.get("mask") or {}
     q = (h @ W[p + "q"].T + W[p + "q.b"]).reshape(T, H, d)
     k = (h @ W[p + "k"].T + W[p + "k.b"]).reshape(T, G, d)
     v = rnd(h @ W[p + "v"].T + W[p + "v.b"]).reshape(T, G, dv)
@@ -182,8 +192,7 @@ def window_attention(h, W, p, m, eps, rnd=_same):
     out = np.zeros((T, H, dv))
     for hh in range(H):
         g = hh // (H // G)
-        out[:, hh] = attend(q[:, hh], k[:, g], v[:, g], m["scale"], m["mask"]["size"], m["mask"]["keep_first"],
-                            float(W[p + "sink"][hh]))
+        out[:, hh] = attend(q[:, hh], k[:, g], v[:, g], m["scale"], mask.get("size"), mask.get("keep_first", 0), float(W[p + "sink"][hh]))
     return rnd(out.reshape(T, H * dv)) @ W[p + "o"].T + W[p + "o.b"]
 
 

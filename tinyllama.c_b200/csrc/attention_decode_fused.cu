@@ -85,7 +85,8 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
                             const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
                             float* __restrict__ part_ml, unsigned* __restrict__ arrivals,
                             __nv_bfloat16* __restrict__ out, int H, int KV, float scale, int window, int n_splits,
-                            int passes, int out_ld, float softcap, int sink) {
+                            int passes, int out_ld, float softcap, int sink, int keep_first,
+                            const float* __restrict__ sink_values) {
   // Keys and values of earlier positions were stored by earlier steps and are fetched before the
   // wait on the previous kernel; the row's own projection is read after it.
   asm volatile("griddepcontrol.launch_dependents;");
@@ -99,13 +100,14 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
   const int pos = positions[t];
   const int n_keys = pos + 1;
   const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
+  const int kept = min(max(keep_first, 0), start);    // with a window, the sequence's first keys stay visible
   const int round = FM_NW * CK;              // keys of one round of the block's warps
   const int span = round * passes;           // keys of this block
   const int kbase = split * span;
   const int n_pg = (span + TLC_PAGE - 1) / TLC_PAGE;
   const int smem_floats = L::FIXED / 4;
   float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;
-  const bool empty = kbase >= n_keys || kbase + span <= start;     // the same for all threads of the block
+  const bool empty = kbase >= n_keys || (kbase + span <= start && kbase >= kept);     // the same for all threads of the block
   __shared__ int s_last;
   if (empty) {
     tlc_wait(ml);
@@ -124,7 +126,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       const int pg0 = kbase / TLC_PAGE;
       for (int j = tid; j < n_pg; j += FM_NT) {
         const int pi = pg0 + j;
-        pages[j] = (pi * TLC_PAGE < n_keys && (pi + 1) * TLC_PAGE > start) ? table[pi] : 0;
+        pages[j] = (pi * TLC_PAGE < n_keys && ((pi + 1) * TLC_PAGE > start || pi * TLC_PAGE < kept)) ? table[pi] : 0;
       }
     }
     __syncthreads();
@@ -136,7 +138,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
     // this warp's chunks: chunk j starts at base_w + j * round
     const int base_w = kbase + w * CK;
     int j_first = 0;
-    if (start - CK - base_w >= 0) j_first = (start - CK - base_w) / round + 1;
+    if (start - CK - base_w >= 0 && base_w >= kept) j_first = (start - CK - base_w) / round + 1;   // (a warp with kept keys walks from them)
     const int j_last = n_keys - 1 - base_w >= 0 ? min(passes - 1, (n_keys - 1 - base_w) / round) : -1;
     // chunk j on its way into its stage (all rows but the row's own position; rows that are no keys of
     // the row are filled with zeros); always closes a group, so that groups can be counted
@@ -149,7 +151,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
         for (int q = lane; q < CK * CPR; q += 32) {
           const int row = q / CPR, c = q % CPR;
           const int key = k0 + row;
-          const bool ok = key >= start && key < n_keys && key != pos;
+          const bool ok = (key >= start || key < kept) && key < n_keys && key != pos;
           const size_t off = ok ? row_offset(key) + (size_t)c * 8 : 0;
           const int dst = row * ROWB + ((c ^ (row & 7)) << 4);
           fm_cp16(Ks + dst, k_pages + off, ok);
@@ -261,7 +263,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           const int key = k0 + n * 8 + cpair + e;
-          const bool valid = key >= start && key < n_keys;
+          const bool valid = (key >= start || key < kept) && key < n_keys;
           float sc = S[n][e] * scale;
           if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);        // a capped score
           S[n][e] = valid ? sc : -INFINITY;
@@ -319,9 +321,10 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       float M = -INFINITY;
 #pragma unroll
       for (int x = 0; x < FM_NW; x++) M = fmaxf(M, m_s[x * 8 + hg]);
-      const bool with_sink = sink && n_splits == 1;       // one more term of score 0 in the sum (splits: at their merge)
-      if (with_sink) M = fmaxf(M, 0.f);
-      float o = 0.f, l = with_sink ? expf(-M) : 0.f;
+      const bool with_sink = sink && n_splits == 1;       // one more term in the sum (splits: at their merge): of score 0,
+      const float sv = (with_sink && sink_values) ? sink_values[g * G + hg] : 0.f;    // or the head's own
+      if (with_sink) M = fmaxf(M, sv);
+      float o = 0.f, l = with_sink ? expf(sv - M) : 0.f;
 #pragma unroll
       for (int x = 0; x < FM_NW; x++) {
         const float mw = m_s[x * 8 + hg];
@@ -351,7 +354,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  attention_merge_splits<HD, FM_NT>(part_o, part_ml, out, reinterpret_cast<float*>(smraw), smem_floats, t, g, G, H, n_splits, out_ld, sink);
+  attention_merge_splits<HD, FM_NT>(part_o, part_ml, out, reinterpret_cast<float*>(smraw), smem_floats, t, g, G, H, n_splits, out_ld, sink, sink_values);
 }
 
 int g_fused_passes = 0;       // > 0: rounds a block takes, for tests (0: chosen from the grid)
@@ -388,7 +391,8 @@ extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, i
                                         const int* block_table, int max_pages, const int* positions,
                                         const int* row_seq, const int* slots, void* out, float* part_o, float* part_ml,
                                         unsigned* arrivals, int T, int H, int KV, int hd, float scale, int window,
-                                        int max_keys, int out_ld, float softcap, int sink, cudaStream_t stream) {
+                                        int max_keys, int out_ld, float softcap, int sink, int keep_first,
+                                        const float* sink_values, cudaStream_t stream) {
   if (T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(tlc_attention_decode_fused_ok(H, KV, hd), "attention(decode, fused): %d heads, %d key/value heads of size %d are outside the kernel's range", H, KV, hd);
@@ -419,7 +423,7 @@ extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, i
 #define TLC_FM_LAUNCH(HDV, CKV, STV)                                                                                   \
   e = launch_fused<HDV, CKV, STV>(grid, passes, stream, qkv, ld, q_off, k_off, v_off, kp, vp, inv_freq, rope_dim, write_kv, \
                                 block_table, max_pages, positions, row_seq, slots, part_o, part_ml, arrivals, op, H, KV, \
-                                scale, window, n_splits, passes, out_ld, softcap, sink)
+                                scale, window, n_splits, passes, out_ld, softcap, sink, keep_first, sink_values)
   if (hd == 64) TLC_FM_LAUNCH(64, 32, 4);
   else if (hd == 128) TLC_FM_LAUNCH(128, 32, 2);
   else TLC_FM_LAUNCH(256, 16, 2);

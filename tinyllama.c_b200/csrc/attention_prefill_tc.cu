@@ -75,7 +75,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int n_tiles, int H,
                             int KV, float scale_log2, int window, int out_ld, int n_split, float* __restrict__ part_o,
-                            float* __restrict__ part_ml, float cap_in, float cap_out, int sink, ErrWords* err) {
+                            float* __restrict__ part_ml, float cap_in, float cap_out, int sink, int keep_first,
+                            const float* __restrict__ sink_values, ErrWords* err) {
   tlc_pdl(out);
   using L_ = FaSmem<HD>;
   constexpr int TCOLS = HD == 128 ? 512 : 256;            // the groups' scores at 0 and 64, their outputs at 128 and 128 + hd
@@ -157,11 +158,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int p0 = start_pos[b] + i0;                       // position of the block's first row
   const int tile_hi_all = (p0 + rows - 1) / BN;
   const int tile_lo_all = window > 0 ? max(0, p0 + 1 - window) / BN : 0;
-  const int per_range = (tile_hi_all - tile_lo_all + n_split) / n_split;             // key tiles of a range, rounded up
-  const int tile_lo = tile_lo_all + key_range * per_range;
-  const int tile_hi = min(tile_hi_all, tile_lo + per_range - 1);
-  const int n = max(0, tile_hi - tile_lo + 1);            // key tiles of this item (none: a range past the tile's keys)
-  for (int i = tid; i < n; i += THREADS) pages[i] = block_table[(size_t)slots[b] * max_pages + tile_lo + i];
+  // with a window, the key tiles that hold the sequence's first keep_first keys stay visible: those of them that lie in
+  // front of the window come first in the item's list of key tiles, then the window's
+  const int n_kept = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, tile_lo_all) : 0;
+  const int n_all = n_kept + tile_hi_all - tile_lo_all + 1;
+  const int per_range = (n_all + n_split - 1) / n_split;                             // key tiles of a range, rounded up
+  const int list_lo = key_range * per_range;
+  const int list_hi = min(n_all - 1, list_lo + per_range - 1);
+  const int n = max(0, list_hi - list_lo + 1);            // key tiles of this item (none: a range past the tile's keys)
+  auto tile_of = [&](int i) { const int at = list_lo + i; return at < n_kept ? at : tile_lo_all + (at - n_kept); };
+  for (int i = tid; i < n; i += THREADS) pages[i] = block_table[(size_t)slots[b] * max_pages + tile_of(i)];
   __syncthreads();
 
   if (warp >= WORKERS / 32) {
@@ -264,12 +270,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           sr[c] = __float_as_uint(fmaf(-cap_out, __fdividef(2.0f, e + 1.0f), cap_out));
         }
       }
-      const int kbase = (tile_lo + j) * BN;
+      const int kbase = tile_of(j) * BN;
       if (window > 0 || kbase + BN - 1 > p0) {
 #pragma unroll
         for (int c = 0; c < 64; c++) {
           const int kp = kbase + c;
-          if (!(kp <= pr && (window <= 0 || kp > pr - window))) sr[c] = 0xff800000u;     // -inf
+          if (!(kp <= pr && (window <= 0 || kp > pr - window || kp < keep_first))) sr[c] = 0xff800000u;     // -inf
         }
       }
       float mx = -INFINITY;
@@ -328,11 +334,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     workers_sync();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool whole = n_split == 1;                      // else the sums stay unnormalised: another kernel adds the ranges
-    const bool with_sink = sink && whole;                 // one more term of score 0 in the denominator (ranges: at the merge)
+    const bool with_sink = sink && whole;                 // one more term in the denominator (ranges: at the merge): of score 0,
+    const float sv = (with_sink && sink_values) ? sink_values[h] * 1.4426950408889634f : 0.f;   // or the head's own (as a power of two)
     const float m0 = xch[r], m1 = xch[BM + r];
-    const float m_all = with_sink ? fmaxf(fmaxf(m0, m1), 0.f) : fmaxf(m0, m1);
+    const float m_all = with_sink ? fmaxf(fmaxf(m0, m1), sv) : fmaxf(m0, m1);
     const float w0 = m0 == -INFINITY ? 0.f : ex2_quick(m0 - m_all), w1 = m1 == -INFINITY ? 0.f : ex2_quick(m1 - m_all);
-    const float l_all = xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1 + (with_sink ? ex2_quick(-m_all) : 0.f);
+    const float l_all = xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1 + (with_sink ? ex2_quick(sv - m_all) : 0.f);
     const float inv = whole ? 1.0f / l_all : 1.0f;
     const float f0 = w0 * inv, f1 = w1 * inv;
     const bool has0 = n > 0, has1 = n > 1;                // the group had a tile at all (else its accumulator was never written)
@@ -387,7 +394,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 constexpr int TC_MAX_SPLIT = 8;
 __global__ void __launch_bounds__(128)
 attention_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                          int H, int hd, int n_split, int out_ld, int sink) {
+                          int H, int hd, int n_split, int out_ld, int sink, const float* __restrict__ sink_values) {
   tlc_pdl(part_o, part_ml, out);
   const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= H) return;
@@ -399,8 +406,9 @@ attention_tc_merge_kernel(const float* __restrict__ part_o, const float* __restr
     lz[z] = z < n_split ? part_ml[(at + z) * 2 + 1] : 0.f;
     if (lz[z] > 0.f) m = fmaxf(m, mz[z]);
   }
-  if (sink) m = fmaxf(m, 0.f);                           // the sink: a range of its own with maximum 0, sum 1 and no values
-  float w[TC_MAX_SPLIT], l = sink ? exp2f(-m) : 0.f;
+  const float sv = (sink && sink_values) ? sink_values[h] * 1.4426950408889634f : 0.f;
+  if (sink) m = fmaxf(m, sv);                            // the sink: a range of its own with its score as maximum, sum 1 and no values
+  float w[TC_MAX_SPLIT], l = sink ? exp2f(sv - m) : 0.f;
 #pragma unroll
   for (int z = 0; z < TC_MAX_SPLIT; z++) {
     w[z] = lz[z] > 0.f ? exp2f(mz[z] - m) : 0.f;
@@ -448,7 +456,7 @@ int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat1
         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
         __nv_bfloat16* out, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
         int p_max, int T, int out_ld, int max_blocks, int n_split, float* part_o, float* part_ml, float softcap, int sink,
-        cudaStream_t stream) {
+        int keep_first, const float* sink_values, cudaStream_t stream) {
   static bool configured = false;
   const int smem = FaSmem<HD>::total(p_max);
   TLC_REQUIRE(smem <= 220 * 1024, "attention(prefill, tcgen05): %d key tiles need %d bytes of shared memory", p_max, smem);
@@ -466,11 +474,11 @@ int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat1
   tlc_launch(attention_prefill_tc_kernel<HD>, dim3(blocks), dim3(THREADS), (size_t)smem, stream, mq, mk, mv,
              block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, n_tiles_bound, H, KV, scale * 1.4426950408889634f,
              window, out_ld, n_split, part_o, part_ml, softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f,
-             softcap > 0.f ? softcap / scale : 0.f, sink, tlc_error_words());
+             softcap > 0.f ? softcap / scale : 0.f, sink, keep_first, sink_values, tlc_error_words());
   TLC_CHECK_LAUNCH("attention(prefill, tcgen05)");
   if (n_split > 1) {
     tlc_launch(attention_tc_merge_kernel, dim3(T, (H + 3) / 4), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, H,
-               HD, n_split, out_ld, sink);
+               HD, n_split, out_ld, sink, sink_values);
     TLC_CHECK_LAUNCH("attention(prefill, tcgen05, merge)");
   }
   return 0;
@@ -503,13 +511,14 @@ extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
 // that many ranges that run as items of their own; part_o [T, H, n_split, hd] and part_ml [T, H, n_split, 2]
 // (32-bit) hold the ranges' results until a second kernel has added them up.
 // softcap > 0: score <- softcap * tanh(score / softcap) after the scale (scale != 0 then); sink: one more term of
-// score 0 in the softmax's denominator, which carries no value.
+// score 0 in the softmax's denominator, which carries no value (sink_values not NULL: of score sink_values[head]).
+// keep_first > 0 with a window: the sequence's first keep_first keys stay visible.
 extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                                         const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                                         int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
-                                        int n_split, float* part_o, float* part_ml, float softcap, int sink,
-                                        cudaStream_t stream) {
+                                        int n_split, float* part_o, float* part_ml, float softcap, int sink, int keep_first,
+                                        const float* sink_values, cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0 || T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;
   TLC_REQUIRE(tlc_attention_prefill_tc_ok(TLC_BF16, hd, H, KV), "attention(prefill, tcgen05): %d heads, %d key/value heads of size %d are not built", H, KV, hd);
@@ -525,7 +534,7 @@ extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, cons
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   if (hd == 64)
     return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, softcap, sink, stream);
+                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, softcap, sink, keep_first, sink_values, stream);
   return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, softcap, sink, stream);
+                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, softcap, sink, keep_first, sink_values, stream);
 }

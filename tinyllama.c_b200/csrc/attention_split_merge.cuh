@@ -7,11 +7,12 @@
 
 // part_o [T, H, n_splits, HD], part_ml [T, H, n_splits, 2]; out: rows of out_ld elements, head h at h * HD;
 // sh: the block's dynamic shared memory of smem_floats floats (free by now); NT threads.  All threads of
-// the block call it.  sink: one more split of maximum 0 and sum 1 that carries no values.
+// the block call it.  sink: one more split of maximum 0 (or sink_values[head]) and sum 1 that carries no values.
 template <int HD, int NT>
 __device__ __forceinline__ void attention_merge_splits(const float* part_o, const float* part_ml, __nv_bfloat16* out,
                                                        float* sh, int smem_floats, int t, int g, int G, int H,
-                                                       int n_splits, int out_ld, int sink = 0) {
+                                                       int n_splits, int out_ld, int sink = 0,
+                                                       const float* sink_values = nullptr) {
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
   constexpr int NW = NT / 32;
   if (2 * G * n_splits <= smem_floats) {
@@ -29,11 +30,12 @@ __device__ __forceinline__ void attention_merge_splits(const float* part_o, cons
       float m = -INFINITY;
       for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, e[2 * s]);
       m = warp_max(m);
-      if (sink) m = fmaxf(m, 0.f);
+      const float sv = (sink && sink_values) ? sink_values[g * G + hg] : 0.f;    // the sink's score: 0, or the head's own
+      if (sink) m = fmaxf(m, sv);
       float l = 0.f;
       for (int s = lane; s < n_splits; s += 32) if (e[2 * s + 1] > 0.f) l += e[2 * s + 1] * expf(e[2 * s] - m);
       l = warp_sum(l);
-      if (sink) l += expf(-m);
+      if (sink) l += expf(sv - m);
       const float inv = 1.0f / l;
       for (int s = lane; s < n_splits; s += 32) e[2 * s] = e[2 * s + 1] > 0.f ? expf(e[2 * s] - m) * inv : 0.f;
     }
@@ -63,8 +65,9 @@ __device__ __forceinline__ void attention_merge_splits(const float* part_o, cons
     const float* mlh = part_ml + th * n_splits * 2;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; s++) m = fmaxf(m, __ldcg(mlh + 2 * s));
-    if (sink) m = fmaxf(m, 0.f);
-    float l = sink ? expf(-m) : 0.f;
+    const float sv = (sink && sink_values) ? sink_values[g * G + hg] : 0.f;
+    if (sink) m = fmaxf(m, sv);
+    float l = sink ? expf(sv - m) : 0.f;
     for (int s = 0; s < n_splits; s++) {
       const float ls = __ldcg(mlh + 2 * s + 1);
       if (ls > 0.f) l += ls * expf(__ldcg(mlh + 2 * s) - m);

@@ -203,7 +203,8 @@ int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, int k_off, i
                                const int* block_table, int max_pages, const int* positions, const int* row_seq,
                                const int* slots, void* out, float* part_o, float* part_ml, unsigned* arrivals,
                                int T, int H, int KV, int hd, float scale, int window, int max_keys, int out_ld,
-                               float softcap, int sink, cudaStream_t stream);
+                               float softcap, int sink, int keep_first,
+                               const float* sink_values, cudaStream_t stream);
 /* Prompt rows (consecutive positions from start_pos) of a bfloat16 cache on the tensor cores. */
 int tlc_attention_prefill_ok(int dtype, int hd);
 int tlc_attention_prefill_chunks(int n_tiles_bound, int H, int max_tiles, int* chunk_tiles /* host */);
@@ -215,13 +216,14 @@ int tlc_attention_prefill(const void* q, const void* k_pages, const void* v_page
 
 /* The same on tcgen05.mma (attention_prefill_tc.cu): 128-row tiles, Q and the K and V pages by TMA, scores and
  * output in tensor memory.  n_tiles_bound >= sum_b ceil(n_new_b / 128); n_pages: pages of k_pages / v_pages.
- * Values in pages past a sequence's end must be finite.  softcap and sink as in tlc_attention. */
+ * Values in pages past a sequence's end must be finite.  softcap, sink, keep_first and sink_values as in tlc_attention. */
 int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV);
 int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                              const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                              const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                              int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
-                             int n_split, float* part_o, float* part_ml, float softcap, int sink, cudaStream_t stream);
+                             int n_split, float* part_o, float* part_ml, float softcap, int sink, int keep_first,
+                             const float* sink_values, cudaStream_t stream);
 int tlc_attention_prefill_tc_splits(int n_tiles_bound, int H, int max_keys);   // suggested n_split (1: none)
 
 /* ---- Mamba2 (mamba.cu, mamba_ssd.cu) ----------------------------------------------------------------- */

@@ -74,14 +74,14 @@ _SIGNATURES = {
     "tlc_attention_decode_fused_ok": (_i, [_i, _i, _i]),
     "tlc_attention_decode_fused_passes": (_i, [_i]),
     "tlc_attention_decode_fused": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp,
-                                        _vp, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _vp]),
+                                        _vp, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _i, _vp, _vp]),
     "tlc_attention_prefill_ok": (_i, [_i, _i]),
     "tlc_attention_prefill_chunks": (_i, [_i, _i, _i, _vp]),
     "tlc_attention_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                    _vp, _i, _i, _vp]),
     "tlc_attention_prefill_tc_ok": (_i, [_i, _i, _i, _i]),
     "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
-                                      _i, _i, _i, _i, _vp, _vp, _f, _i, _vp]),
+                                      _i, _i, _i, _i, _vp, _vp, _f, _i, _i, _vp, _vp]),
     "tlc_attention_prefill_tc_splits": (_i, [_i, _i, _i]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
                             _i, _i, _i, _i, _i, _i, _vp]),
@@ -678,7 +678,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     own_softmax = softcap > 0 or sink
     tiled = decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
         and hd in (64, 128) and not DISABLE_TILED_ATTENTION
-    if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 and keep_first == 0 and sink_values is None \
+    if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
             and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
         B = slots.numel()
         # few row tiles and many keys (a piece of a long prompt): the keys in ranges that run side by side
@@ -690,7 +690,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_prefill_tc", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
               block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(),
               out.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
-              out_ld, int(max_blocks), int(n_split), _p(part_o), _p(part_ml), float(softcap), int(bool(sink)), _stream())
+              out_ld, int(max_blocks), int(n_split), _p(part_o), _p(part_ml), float(softcap), int(bool(sink)), keep_first,
+              _p(sink_values), _stream())
         return
     if tiled and not own_softmax and keep_first == 0:
         B = slots.numel()
@@ -735,12 +736,16 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
                            v_pages: torch.Tensor, inv_freq: torch.Tensor, write_kv: bool, block_table: torch.Tensor,
                            positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
                            H: int, KV: int, hd: int, scale: float, window: int, max_keys: int,
-                           arrivals: torch.Tensor, softcap: float = 0.0, sink: bool = False) -> None:
+                           arrivals: torch.Tensor, softcap: float = 0.0, sink: bool = False, keep_first: int = 0,
+                           sink_values: Optional[torch.Tensor] = None) -> None:
     """Single-token steps in one kernel: rotates the row's queries and new key (2 * len(inv_freq)
     leading dims of each head), stores the new key/value row into its page when write_kv, attends
     over the sequence's pages and writes out [T, H*hd] bfloat16.  qkv is float32 with dense rows.
-    arrivals: the caller's counters (new_arrival_counters).  softcap and sink as in attention()."""
-    _gpu(qkv, k_pages, v_pages, inv_freq, block_table, positions, row_seq, slots, out)
+    arrivals: the caller's counters (new_arrival_counters).  softcap, sink, keep_first and sink_values as in attention()."""
+    _gpu(qkv, k_pages, v_pages, inv_freq, block_table, positions, row_seq, slots, out, sink_values)
+    if sink_values is not None:
+        _f32vec(sink_values, H, "attention sink scores")
+        sink = True
     T = qkv.shape[0]
     for t, n in ((positions, "positions"), (row_seq, "row_seq"), (slots, "slots"), (block_table, "block_table")):
         _i32(t, n)
@@ -767,7 +772,7 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),
           part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), out_ld,
-          float(softcap), int(bool(sink)), _stream())
+          float(softcap), int(bool(sink)), int(keep_first) if window else 0, _p(sink_values), _stream())
 
 
 def attention_decode_fused_passes(passes: int) -> None:

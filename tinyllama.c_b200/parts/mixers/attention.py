@@ -250,14 +250,13 @@ class AttentionMixer(Part):
         joined = out
         if self.maps > 1:             # the kernels write the maps' results; the join writes the heads'
             out = None
-        if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd) \
-                and not (self.keep_first or self.sink_values is not None):
+        if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
             att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
                                        self.H, self.KV, self.hd, self.scale, self.window or 0,
-                                       step.max_context, self._arrivals, self.softcap, self.sink)
+                                       step.max_context, self._arrivals, self.softcap, self.sink, self.keep_first, self.sink_values)
             return self._joined(self._gated(att, qkv), joined)
         q = scratch_buf(f"attention.{self.cache_key}.q", (T, self.H * self.hd), self.dtype, qkv.device)
         ops.rope_kv_store(qkv, self.q_off, self.k_off, self.v_off, q, kv.k_pages, kv.v_pages, table, step.positions,
