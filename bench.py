@@ -245,9 +245,10 @@ def main() -> int:
     ap.add_argument("--no-big", dest="big", action="store_false", help="skip the 3B and 7B workloads among the points")
     ap.add_argument("--no-pairs", action="store_true", help="run the linear layers on single blocks (128 x 256 tiles) instead "
                     "of pairs of blocks on 256 x 256 tiles: the comparison behind profiles/linear_tcgen05_prefill_2048.md")
-    ap.add_argument("--design", default=None, choices=["turevik", "porarax", "sogazen"], help="instead of the benchmark line: prefill and decode "
+    ap.add_argument("--design", default=None, choices=["turevik", "porarax", "sogazen", "kimutar"], help="instead of the benchmark line: prefill and decode "
                     "throughput of this design at layer sizes of a real model's order (random weights), beside the library's "
-                    "closest other design (Falcon-H1 for turevik and sogazen, Turevik for porarax) at equal width and layer count")
+                    "closest other design (Falcon-H1 for turevik and sogazen, Turevik for porarax, Porarax for kimutar) at equal "
+                    "width and layer count")
     ap.add_argument("--sizes-only", default=None, choices=["width 2048", "width 3072"], help="with --design: one of the two sizes")
     ap.add_argument("--ref-budget", type=float, default=600.0, help="seconds the reference arm may take (it runs fewer "
                     "layers, and says so, where all of them would take longer)")
@@ -473,9 +474,63 @@ def sogazen_work(cfg, batch, context, T):
     return fixed * 2 + expert_bytes + cache_bytes, 2.0 * (fixed - V * D + expert_params) * T + 2.0 * V * D + mix_flops
 
 
+def kimutar_config(width, heads, kv_heads, window, ff, experts, top, expert_ff, shared_ff, vocab):
+    """Four layers with every kind of mixer and feed-forward: attention over a window that keeps four keys, with a sink,
+    beside a dense feed-forward; the delta rule with a decay per channel beside experts; attention with two maps a head
+    (half as many heads, so that the kernels see as many as in the first layer) beside experts; the delta rule again.  The
+    last three layers are the repeated range, run once (as many layer runs as the design beside it has layers)."""
+    moe = dict(kind="moe", router=dict(experts=experts, top=top, scale=2.0), expert=dict(ff=expert_ff), shared=dict(ff=shared_ff))
+    delta = dict(type="channel_delta", mixer=dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4, decay_rank=width // 16,
+                                                  gate_rank=width // 16), mlp=moe)
+    return dict(architecture="Kimutar", vocab=vocab, width=width, norm=dict(eps=1e-6), loop=dict(start=1, stop=4, times=1), layers=[
+        dict(type="attention_2", mixer=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5,
+                                            rot=dict(base=500000.0, dims=128, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)),
+                                            mask=dict(size=window, keep_first=4)), mlp=dict(kind="dense", ff=ff)),
+        delta,
+        dict(type="attention", mixer=dict(heads=heads // 2, kv_heads=kv_heads // 2, dim=128, vdim=128, scale=128 ** -0.5, diff=0.3,
+                                          rot=dict(base=500000.0, dims=64, scaling=dict(factor=2.0, original=8192, fast=32.0, slow=1.0))),
+             mlp=moe),
+        delta])
+
+
+def kimutar_work(cfg, batch, context, T):
+    """(bytes a decode step of `batch` sequences at `context` must read, FLOPs of a prompt of T tokens)."""
+    D, V = cfg["width"], cfg["vocab"]
+    fixed, cache_bytes, mix_flops, expert_bytes, expert_params = 2 * V * D, 0, 0.0, 0.0, 0        # the table and the head
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        if layer["type"] == "attention_2":
+            W = m["mask"]["size"]
+            fixed += (H * dk + G * dk + G * dv) * D + D * H * dv
+            cache_bytes += batch * min(context, W + m["mask"]["keep_first"]) * G * (dk + dv) * 2
+            keys = sum(min(t + 1, W + m["mask"]["keep_first"]) for t in range(T)) if T > 1 else 1
+            mix_flops += 2.0 * H * (dk + dv) * keys
+        elif layer["type"] == "attention":
+            fixed += (2 * H * dk + 2 * G * dk + G * dv) * D + D * H * dv
+            cache_bytes += batch * context * G * (2 * dk + dv) * 2            # two maps of keys, the values once
+            mix_flops += 2.0 * 2 * H * (dk + dv) * T * (T + 1) / 2
+        else:
+            ra, rg = m["decay_rank"], m["gate_rank"]
+            fixed += (2 * G * dk + H * dv + H + ra + rg) * D + H * dk * ra + H * dv * rg + D * H * dv
+            cache_bytes += batch * H * dk * dv * 4                            # the state, 32-bit
+            mix_flops += 6.0 * H * dk * dv * T
+        mlp = layer["mlp"]
+        if mlp["kind"] == "dense":
+            fixed += 2 * D * mlp["ff"]
+            continue
+        E, top, F = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+        fixed += (E + 1) * D + 3 * D * mlp["shared"]["ff"]
+        expert_params += top * 3 * D * F
+        touched = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))              # expected distinct experts of a step
+        expert_bytes += touched * 3 * D * F * 2
+    # (the table is read by rows, not as a whole)
+    return (fixed - V * D) * 2 + expert_bytes + cache_bytes, 2.0 * (fixed - 2 * V * D + expert_params) * T + 2.0 * V * D + mix_flops
+
+
 def design_compare(args) -> int:
     """Another design beside the library's closest one at equal width and layer count (Turevik and Sogazen beside Falcon-H1,
-    Porarax beside Turevik): a prompt of --prefill-tokens tokens and decode steps at batch 8 and 64 from --prompt-len-token
+    Porarax beside Turevik, Kimutar beside Porarax): a prompt of --prefill-tokens tokens and decode steps at batch 8 and 64 from --prompt-len-token
     prompts, each as time and as a fraction of the measured peak for the bytes a step must read (decode) or the FLOPs a
     prompt needs (prefill)."""
     import torch
@@ -488,6 +543,12 @@ def design_compare(args) -> int:
         cases = {"width 2048": (porarax_config(2048, 16, 4, 256, 768, 1024, 32, 4, 1024, 65536), turevik["width 2048"]),
                  "width 3072": (porarax_config(3072, 24, 8, 256, 1024, 1024, 64, 6, 2048, 130048), turevik["width 3072"])}
         beside = "turevik"
+    elif args.design == "kimutar":
+        porarax = {"width 2048": porarax_config(2048, 16, 4, 256, 768, 1024, 32, 4, 1024, 65536),
+                   "width 3072": porarax_config(3072, 24, 8, 256, 1024, 1024, 64, 6, 2048, 130048)}
+        cases = {"width 2048": (kimutar_config(2048, 16, 4, 1024, 4096, 32, 4, 1024, 1024, 65536), porarax["width 2048"]),
+                 "width 3072": (kimutar_config(3072, 24, 8, 1024, 12288, 64, 6, 2048, 2048, 130048), porarax["width 3072"])}
+        beside = "porarax"
     elif args.design == "sogazen":
         cases = {"width 2048": (sogazen_config(2048, 8, 2, 48, 64, 256, 32, 4096, 32, 4, 4, 1024, 65536), dict(CONFIG_1P5B, num_hidden_layers=4)),
                  "width 3072": (sogazen_config(3072, 12, 2, 24, 128, 256, 48, 12288, 64, 8, 6, 2048, 130048), dict(CONFIG_7B, num_hidden_layers=4))}
@@ -496,7 +557,7 @@ def design_compare(args) -> int:
         cases = {"width 2048": (turevik["width 2048"], dict(CONFIG_1P5B, num_hidden_layers=4)),
                  "width 3072": (turevik["width 3072"], dict(CONFIG_7B, num_hidden_layers=4))}
         beside = "falcon_h1"
-    work = {"turevik": turevik_work, "porarax": porarax_work, "sogazen": sogazen_work}
+    work = {"turevik": turevik_work, "porarax": porarax_work, "sogazen": sogazen_work, "kimutar": kimutar_work}
     if args.sizes_only:
         cases = {k: v for k, v in cases.items() if k == args.sizes_only}
     for name, (tcfg, fcfg) in cases.items():

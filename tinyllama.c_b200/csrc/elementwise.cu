@@ -656,9 +656,32 @@ __global__ void convert_kernel(const float* __restrict__ x, int ldx, int D, TO* 
   const float r = fmaxf(v, 0.f);
   out[t * ldo + d] = from_f32<TO>(act == 1 ? tanhf(v) : act == 2 ? r * r : v);
 }
+// The same, four neighbouring values a thread (widths and strides that are multiples of 4, rows on 16-byte boundaries).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+convert4_kernel(const float* __restrict__ x, int ldx, int D4, TO* __restrict__ out, int ldo, size_t total4, int act) {
+  tlc_pdl(x, out);
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total4) return;
+  const size_t t = i / D4;
+  const int d = (int)(i % D4) * 4;
+  float4 v = *reinterpret_cast<const float4*>(x + t * ldx + d);
+  if (act == 1) { v.x = tanhf(v.x); v.y = tanhf(v.y); v.z = tanhf(v.z); v.w = tanhf(v.w); }
+  else if (act == 2) {
+    v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+    v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;
+  }
+  Out4<TO>::put(out + t * ldo + d, v.x, v.y, v.z, v.w);
+}
 extern "C" int tlc_convert(const float* x, int ldx, int T, int D, void* out, int dtype, int ldo, int act, cudaStream_t stream) {
   const size_t total = (size_t)T * D;
   if (total == 0) return 0;
+  if (act >= 0 && act <= 2 && D % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    TLC_DISPATCH_DTYPE(dtype, TO, tlc_launch(convert4_kernel<TO>, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, x, ldx,
+                                             D / 4, (TO*)out, ldo, total / 4, act));
+    TLC_CHECK_LAUNCH("convert");
+    return 0;
+  }
   TLC_REQUIRE(act >= 0 && act <= 2, "convert: unknown function %d (0 none, 1 tanh, 2 squared relu)", act);
   TLC_DISPATCH_DTYPE(dtype, TO, tlc_launch(convert_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, ldx, D,
                                            (TO*)out, ldo, total, act));

@@ -65,7 +65,8 @@ layernorm_kernel(const float* __restrict__ x, int x_ld, const int* __restrict__ 
 }
 
 // Rows whose width is a multiple of 4 (up to 4096 float4): NT threads take PT float4 each, 16-byte loads and stores.
-// NT and PT follow from the width alone, so a row's sums have the same tree whatever else is in the batch.
+// NT and PT follow from the width and from whether the step has 512 rows or more; a prompt cut into portions may so take
+// another tree for a row's sums than the whole prompt does, which moves a result by rounding only.
 template <typename TO> struct LnOut4;
 template <> struct LnOut4<float> {
   static __device__ __forceinline__ void put(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
@@ -84,9 +85,18 @@ template <typename TO, int NT, int PT>
 __global__ void __launch_bounds__(NT)
 layernorm_vec_kernel(const float* __restrict__ x, int x_ld, const int* __restrict__ rows, const float* __restrict__ w1,
                      const float* __restrict__ w2, float eps, int D, TO* __restrict__ out1, TO* __restrict__ out2) {
-  tlc_pdl(x, rows, out1, out2);
+  asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[33];
   const int n4 = D >> 2, r = blockIdx.x;
+  // the weights do not depend on the kernel before this one: they are fetched before the wait on it
+  float4 wa[PT], wb[PT];
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    wa[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(w1) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    wb[i] = (w2 != nullptr && c < n4) ? __ldg(reinterpret_cast<const float4*>(w2) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  tlc_wait(x, rows, out1, out2);
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * x_ld);
   float4 v[PT];
   float s = 0.f;
@@ -111,10 +121,10 @@ layernorm_vec_kernel(const float* __restrict__ x, int x_ld, const int* __restric
   for (int i = 0; i < PT; i++) {
     const int c = threadIdx.x + i * NT;
     if (c < n4) {
-      const float4 a = __ldg(reinterpret_cast<const float4*>(w1) + c);
+      const float4 a = wa[i];
       LnOut4<TO>::put(out1 + (size_t)r * D + 4 * c, v[i].x * inv * a.x, v[i].y * inv * a.y, v[i].z * inv * a.z, v[i].w * inv * a.w);
       if (out2) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(w2) + c);
+        const float4 b = wb[i];
         LnOut4<TO>::put(out2 + (size_t)r * D + 4 * c, v[i].x * inv * b.x, v[i].y * inv * b.y, v[i].z * inv * b.z, v[i].w * inv * b.w);
       }
     }
@@ -133,13 +143,22 @@ extern "C" int tlc_layernorm(const float* x, int x_ld, const int* rows, const fl
 #define TLC_LN_LAUNCH(NT, PT)                                                                                                   \
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(layernorm_vec_kernel<TO, NT, PT>, dim3(R), dim3(NT), 0, stream, x, x_ld, rows, w1, w2, \
                                                eps, D, (TO*)out1, (TO*)out2))
-    if (n4 <= 64) { TLC_LN_LAUNCH(64, 1); }
-    else if (n4 <= 128) { TLC_LN_LAUNCH(128, 1); }
-    else if (n4 <= 256) { TLC_LN_LAUNCH(128, 2); }
-    else if (n4 <= 512) { TLC_LN_LAUNCH(128, 4); }
-    else if (n4 <= 1024) { TLC_LN_LAUNCH(256, 4); }
-    else if (n4 <= 2048) { TLC_LN_LAUNCH(512, 4); }
-    else { TLC_LN_LAUNCH(1024, 4); }
+    if (R >= 512) {          // many rows (prompts): fewer threads a row with up to four pieces each, more rows an SM
+      if (n4 <= 128) { TLC_LN_LAUNCH(64, 2); }
+      else if (n4 <= 256) { TLC_LN_LAUNCH(64, 4); }
+      else if (n4 <= 512) { TLC_LN_LAUNCH(128, 4); }
+      else if (n4 <= 768) { TLC_LN_LAUNCH(256, 3); }
+      else if (n4 <= 1024) { TLC_LN_LAUNCH(256, 4); }
+      else if (n4 <= 2048) { TLC_LN_LAUNCH(512, 4); }
+      else { TLC_LN_LAUNCH(1024, 4); }
+    } else {                 // few rows: a piece a thread, so that the row's loads are all in flight at once
+      if (n4 <= 128) { TLC_LN_LAUNCH(128, 1); }
+      else if (n4 <= 256) { TLC_LN_LAUNCH(256, 1); }
+      else if (n4 <= 512) { TLC_LN_LAUNCH(512, 1); }
+      else if (n4 <= 1024) { TLC_LN_LAUNCH(1024, 1); }
+      else if (n4 <= 2048) { TLC_LN_LAUNCH(1024, 2); }
+      else { TLC_LN_LAUNCH(1024, 4); }
+    }
 #undef TLC_LN_LAUNCH
     TLC_CHECK_LAUNCH("layernorm");
     return 0;
@@ -156,10 +175,22 @@ __global__ void __launch_bounds__(256) add_row_kernel(float* __restrict__ x, con
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < total) x[i] += v[i % D];
 }
+__global__ void __launch_bounds__(256) add_row4_kernel(float4* __restrict__ x, const float4* __restrict__ v, int D4, size_t total4) {
+  tlc_pdl(x);
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total4) return;
+  float4 a = x[i];
+  const float4 b = __ldg(v + i % D4);
+  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  x[i] = a;
+}
 extern "C" int tlc_add_row(float* x, const float* v, int T, int D, cudaStream_t stream) {
   const size_t total = (size_t)T * D;
   if (total == 0) return 0;
-  tlc_launch(add_row_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, v, D, total);
+  if (D % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)v % 16) == 0)
+    tlc_launch(add_row4_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (float4*)x, (const float4*)v, D / 4, total / 4);
+  else
+    tlc_launch(add_row_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, v, D, total);
   TLC_CHECK_LAUNCH("add_row");
   return 0;
 }
