@@ -329,20 +329,20 @@ def kimutar_random(seed: int) -> dict:
         kv = pick(1, 2, 3)
         heads = kv * pick(1, 2, 3, 5)
         if kind == "channel_delta":
-            layers.append(_k_delta(heads, kv, pick(4, 8, 20, 32, 40, 64), pick(8, 12, 32, 40), pick(1, 2, 3, 4, 6), pick(3, 8, 16), pick(2, 8, 24), mlp))
+            layers.append(_k_delta(heads, kv, pick(4, 8, 10, 20, 32, 40, 64), pick(6, 8, 12, 32, 40), pick(1, 2, 3, 4, 6), pick(3, 8, 16), pick(2, 8, 24), mlp))
             continue
-        dim, vdim = pick(8, 16, 24, 32, 64), pick(8, 16, 32, 64)
+        dim, vdim = pick(8, 10, 16, 24, 32, 64), pick(6, 8, 16, 20, 32, 64)
         dims = pick(0, 2, dim // 4 * 2, dim)
         scale = float(dim ** -0.5 * rng.uniform(0.5, 2.0))
         if kind == "attention":
             sc = pick(None, dict(factor=pick(2.0, 6.0), original=pick(32, 100), fast=pick(8.0, 32.0), slow=pick(1.0, 2.0)))
-            layers.append(_k_diff(heads, kv, dim, vdim, scale, pick(0.1, 0.3, 0.6), _k_rot(pick(50.0, 10000.0, 250000.0), dims, **(sc or {})), mlp))
+            layers.append(_k_diff(heads, kv, dim, vdim, scale, pick(0.1, 0.3, 0.6), _k_rot(pick(50.0, 10000.0, 500000.0), dims, **(sc or {})), mlp))
         else:
             sc = pick(None, dict(factor=pick(2.0, 8.0), original=pick(32, 100), low=pick(1.0, 2.0), high=pick(3.0, 4.0)))
             size = pick(None, 1, 7, 40, 64, 90)
-            layers.append(_k_window(heads, kv, dim, vdim, scale, _k_rot(pick(50.0, 10000.0, 250000.0), dims, **(sc or {})), size,
+            layers.append(_k_window(heads, kv, dim, vdim, scale, _k_rot(pick(50.0, 10000.0, 500000.0), dims, **(sc or {})), size,
                                     pick(0, 1, 4, 66) if size else 0, mlp))
-    cfg = dict(architecture="Kimutar", vocab=pick(50, 131, 300), width=pick(32, 44, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)), layers=layers)
+    cfg = dict(architecture="Kimutar", vocab=pick(50, 131, 300), width=pick(32, 44, 50, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)), layers=layers)
     if rng.random() < 0.7:
         start = int(rng.integers(0, len(layers)))
         cfg["loop"] = dict(start=start, stop=int(rng.integers(start + 1, len(layers) + 1)), times=pick(1, 2, 3))

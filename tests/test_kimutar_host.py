@@ -69,6 +69,15 @@ def test_without_a_repeated_range_and_without_window_or_scaling():
     assert m.layers[2].mixers[0].position.scaling["kind"] == "ramp"
 
 
+def test_a_stored_norm_of_a_feed_forward_that_is_not_there_is_no_fault():
+    from tinyllama_c_b200.weights.loader import WeightError, check_tensors, random_tensors
+    m = build(configs.KIMUTAR_A)
+    tensors = random_tensors(m, 1)
+    check_tensors(m, dict(tensors, **{"l2.norm2": torch.ones(52)}))
+    with pytest.raises(WeightError, match="l1.norm3"):
+        check_tensors(m, dict(tensors, **{"l1.norm3": torch.ones(52)}))
+
+
 def test_sizes_that_only_stored_tensors_give():
     cfg = copy.deepcopy(configs.KIMUTAR_A)
     del cfg["layers"][0]["mixer"]["decay_rank"], cfg["layers"][0]["mixer"]["gate_rank"]
@@ -110,7 +119,7 @@ def test_configuration_faults_are_named(edit, text):
 
 
 # ---- pieces of the library that need no kernel -------------------------------------------------------------------------------
-@pytest.mark.parametrize("base,dims,sc", [(250000.0, 24, dict(factor=2.0, original=2048, fast=32.0, slow=1.0)),
+@pytest.mark.parametrize("base,dims,sc", [(500000.0, 40, dict(factor=3.0, original=1024, fast=16.0, slow=2.0)),
                                           (100.0, 8, dict(factor=4.0, original=64, fast=8.0, slow=2.0)),
                                           (10000.0, 64, dict(factor=40.0, original=4096, fast=32.0, slow=1.0)),
                                           (50.0, 2, dict(factor=3.0, original=10, fast=1.0, slow=1.0))])
@@ -123,7 +132,7 @@ def test_frequencies_blended_along_a_ramp(base, dims, sc):
     assert np.all(want <= plain_f * (1 + 1e-12)) and np.all(want >= plain_f / sc["factor"] * (1 - 1e-12))
 
 
-@pytest.mark.parametrize("base,dims,sc", [(250000.0, 96, dict(factor=8.0, low=1.0, high=4.0, original=2048)),
+@pytest.mark.parametrize("base,dims,sc", [(300000.0, 80, dict(factor=6.0, low=1.0, high=3.0, original=1024)),
                                           (10000.0, 16, dict(factor=3.0, low=1.0, high=5.0, original=50)),
                                           (500000.0, 128, dict(factor=32.0, low=1.0, high=4.0, original=8192))])
 def test_frequencies_kept_divided_or_blended_by_wave_length(base, dims, sc):

@@ -105,8 +105,11 @@ def run_order(cfg: KimutarConfig) -> List[LayerRun]:
 
 def build(cfg: KimutarConfig) -> Model:
     tables = {LOOP_TABLE: cfg.loop["times"]} if cfg.loop is not None else None
+    # a layer without a feed-forward has no use for the feed-forward's norm, stored or not; nor a model without a repeated
+    # range for the table of its passes
+    unused = [f"l{i}.norm2" for i, layer in enumerate(cfg.layers) if layer.get("mlp") is None] + ([LOOP_TABLE] if cfg.loop is None else [])
     return Model(cfg, layer_specs(cfg), run_order(cfg), _norm(cfg, "final.norm"), embed_name="embed", head_name="head",
-                 vocab=cfg.vocab, hidden=cfg.width, row_tables=tables)
+                 vocab=cfg.vocab, hidden=cfg.width, row_tables=tables, unused_tensors=unused)
 
 
 register_architecture("Kimutar", KimutarConfig, build)

@@ -23,8 +23,9 @@ class Model:
     def __init__(self, config, layer_specs: Sequence[LayerSpec], schedule: Optional[Sequence[LayerRun]],
                  final_norm: PartSpec, embed_name: str, head_name: Optional[str], vocab: int, hidden: int,
                  embed_scale: float = 1.0, head_scale: float = 1.0, logit_softcap: float = 0.0,
-                 row_tables: Optional[Dict[str, int]] = None):
-        """row_tables: learned tables [rows, hidden] by tensor name -> number of rows; an entry of the run order may name a
+                 row_tables: Optional[Dict[str, int]] = None, unused_tensors: Sequence[str] = ()):
+        """unused_tensors: names that a model folder may hold although this model reads none of them (the loader does not
+        call them unexpected).  row_tables: learned tables [rows, hidden] by tensor name -> number of rows; an entry of the run order may name a
         row that is added to the residual stream before it runs (LayerRun.add)."""
         self.config = config
         self.vocab, self.hidden = int(vocab), int(hidden)
@@ -64,6 +65,7 @@ class Model:
         self.logit_softcap = float(logit_softcap)          # > 0: logits <- cap * tanh(logits / cap)
         self.head = StackedLinear(hidden)
         self.head.add(head_name or embed_name, vocab, None, 1.0, head_scale)
+        self.unused_tensors = frozenset(unused_tensors)
         self.row_tables = {k: int(v) for k, v in (row_tables or {}).items()}
         self.rows_of: Dict[str, torch.Tensor] = {}
         self.embed_table: Optional[torch.Tensor] = None

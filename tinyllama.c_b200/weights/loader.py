@@ -44,7 +44,8 @@ def build_model(config: ModelConfig) -> Model:
 def check_tensors(model: Model, tensors: Dict[str, torch.Tensor]) -> None:
     specs = {s.name: s for s in model.weight_specs()}
     missing = sorted(n for n in specs if n not in tensors)
-    unexpected = sorted(n for n in tensors if n not in specs)
+    # (tensors a model says it has no use for, but that a writer may store all the same, are no fault)
+    unexpected = sorted(n for n in tensors if n not in specs and n not in getattr(model, "unused_tensors", ()))
     wrong = []
     for n, s in specs.items():
         if n in tensors and tuple(tensors[n].shape) != tuple(s.shape):
