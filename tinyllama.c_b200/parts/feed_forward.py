@@ -106,6 +106,16 @@ class DenseFeedForward(Part):
         ops.convert(u, act, self.act)
         self.down.forward(act, residual, accumulate=accumulate)
 
+    def forward_parts(self, normed: torch.Tensor):
+        """(the result as one term float32 [T, 1, D], None, None), for a block that runs this feed-forward beside its mixers
+        and adds its terms afterwards (add_parts)."""
+        out = scratch_buf("mlp.out", (normed.shape[0], 1, self.hidden), torch.float32, normed.device)
+        self.forward(normed, out[:, 0], accumulate=False)
+        return out, None, None
+
+    def add_parts(self, terms, residual: torch.Tensor, accumulate: bool = True) -> None:
+        ops.rmsnorm_add(terms[0], None, 0.0, residual, None, None, gate_sigmoid=True, accumulate=accumulate)
+
 
 @register_feed_forward("moe")
 class MoEFeedForward(Part):
